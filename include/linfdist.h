@@ -1,0 +1,168 @@
+/*
+ * linfdist.h -- C ABI of liblinfdist.so: the L_p / L_inf-distance neuron on B200 (sm_100a).
+ *
+ * The library is the device-side replacement for the torch extension `norm_dist_cpp`
+ * of zbh2047/L_inf-dist-net (binding file model/norm_dist.cpp).  Every entry point takes
+ * plain device pointers and integer sizes; nothing in a signature is a torch type.
+ *
+ * Tensor layout (identical to the reference, all contiguous, fp32 unless noted):
+ *     input / lower / upper / grad_input   [B, CI, HW]
+ *     weight / grad_weight                 [CO, CI/G]
+ *     output / pos(int32) / grad_output    [B, CO, HW]
+ * B batch, CI input channels, CO output channels, G groups, HW spatial positions
+ * (1 for a dense layer).  Group g maps input channels [g*CI/G, (g+1)*CI/G) to output
+ * channels [g*CO/G, (g+1)*CO/G).
+ *
+ * Common rules
+ *   - every pointer is a DEVICE pointer on the current device; the caller owns all
+ *     buffers; the entry points of this header that take no workspace allocate nothing;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream); calls
+ *     are asynchronous with respect to the host;
+ *   - the return value is 0 on success or one of the LINF_ERR_* codes; no entry point
+ *     ever traps or asserts on the device;
+ *   - the library keeps no mutable global state besides cached per-device attributes,
+ *     so calls from several host threads are safe.
+ */
+#ifndef LINFDIST_H_
+#define LINFDIST_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LINF_OK             0
+#define LINF_ERR_NULL       1   /* a required pointer is NULL                           */
+#define LINF_ERR_DIMS       2   /* a dimension is <= 0 or a product overflows int32     */
+#define LINF_ERR_GROUP      3   /* CI or CO is not a multiple of G                      */
+#define LINF_ERR_P          4   /* p is NaN, infinite or <= 1 (finite-p entry points)   */
+#define LINF_ERR_LAUNCH     5   /* the CUDA runtime reported an error at launch         */
+#define LINF_ERR_WORKSPACE  6   /* workspace missing, misaligned or too small           */
+#define LINF_ERR_TOO_LARGE  7   /* size beyond a documented fixed maximum               */
+
+/* Library version as major*10000 + minor*100 + patch. */
+int linf_version(void);
+
+/* Static text for a LINF_ERR_* code (never NULL). */
+const char* linf_error_string(int code);
+
+/* ---------------------------------------------------------------------------------
+ * p = inf
+ * --------------------------------------------------------------------------------- */
+
+/*
+ * output[b,o,hw] = max_i |input[b,g,i,hw] - weight[o,i]|
+ * pos[b,o,hw]    = i* | (sign << 31), i* = LOWEST index (within the group) attaining the
+ *                  maximum, sign = 1 iff input - weight < 0 there; an all-zero (or all-NaN)
+ *                  row gives output 0, pos 0.
+ * Replaces inf_dist_forward_cuda (model/norm_dist.cpp:13-14, called at :54-62; kernel
+ * model/inf_dist_cuda.cu:10-68, launcher :173-180).  Values and pos are bit-identical.
+ */
+int linf_inf_dist_forward(const float* input, const float* weight,
+                          int B, int CO, int CI, int G, int HW,
+                          float* output, int* pos, void* stream);
+
+/*
+ * Same result, but the caller lends scratch memory so that the k-range of a layer can be
+ * split across SMs when there are too few output tiles to fill the GPU.  `workspace`
+ * must be 256-byte aligned and at least linf_inf_dist_forward_workspace_bytes(...) long
+ * (the query returns 0 when the shape never needs scratch; then workspace may be NULL).
+ * The workspace is written and read inside this call only; two calls that overlap on the
+ * GPU must not share it.
+ */
+size_t linf_inf_dist_forward_workspace_bytes(int B, int CO, int CI, int G, int HW);
+int linf_inf_dist_forward_ws(const float* input, const float* weight,
+                             int B, int CO, int CI, int G, int HW,
+                             float* output, int* pos,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Interval propagation through an inf-dist layer in one pass:
+ *   tL = lower - w, tU = upper - w
+ *   output_upper = max_i max(|tL|, |tU|)
+ *   output_lower = max_i ( (tL < 0 && tU > 0) ? 0 : min(|tL|, |tU|) )
+ * Both start from 0.  Replaces inf_dist_bound_forward_cuda (model/norm_dist.cpp:15-16,
+ * :64-74; kernel model/inf_dist_cuda.cu:73-141, launcher :181-188).  Bit-identical for
+ * every input, including lower > upper.
+ */
+int linf_inf_dist_bound_forward(const float* input_lower, const float* input_upper,
+                                const float* weight,
+                                int B, int CO, int CI, int G, int HW,
+                                float* output_lower, float* output_upper, void* stream);
+
+/*
+ * grad_input[b, g*CI/G + idx, hw] = sum over o of (pos >= 0 ? +g : -g), g = grad_output[b,o,hw],
+ * idx = pos & 0x7fffffff.  The sum runs in ASCENDING o, one fp32 add at a time starting from
+ * +0, so the result is the same on every run.  grad_input is fully overwritten (it need
+ * not be zeroed).  Replaces inf_dist_backward_input_cuda (model/norm_dist.cpp:17-18,
+ * :76-82; kernel model/inf_dist_cuda.cu:143-156, launcher :189-196), whose atomicAdd
+ * order is undefined: this is one of the orders it can produce.
+ */
+int linf_inf_dist_backward_input(const float* grad_output, const int* pos,
+                                 int B, int CO, int CI, int G, int HW,
+                                 float* grad_input, void* stream);
+
+/*
+ * grad_weight[o, idx] = sum over (b, hw) of (pos < 0 ? +g : -g), in ASCENDING b*HW + hw
+ * order, sequential fp32 adds from +0.  grad_weight is fully overwritten.  Replaces
+ * inf_dist_backward_weight_cuda (model/norm_dist.cpp:19-20, :84-90; kernel
+ * model/inf_dist_cuda.cu:158-171, launcher :197-204).
+ */
+int linf_inf_dist_backward_weight(const float* grad_output, const int* pos,
+                                  int B, int CO, int CI, int G, int HW,
+                                  float* grad_weight, void* stream);
+
+/*
+ * Both gradients in one pass over (grad_output, pos) with warp-aggregated fp32 atomics:
+ * contributions of one warp that hit the same address are summed in lane order first and
+ * issued as one atomic.  The buffers are ACCUMULATED into, exactly like the reference
+ * kernels (model/inf_dist_cuda.cu:143-171): the caller zero-fills them.  Either gradient
+ * pointer may be NULL to skip it.  The order of atomics across warps is undefined, so a
+ * cell that receives three or more contributions may differ in the last bit from the
+ * ordered entry points above.
+ */
+int linf_inf_dist_backward_atomic(const float* grad_output, const int* pos,
+                                  int B, int CO, int CI, int G, int HW,
+                                  float* grad_input, float* grad_weight, void* stream);
+
+/* ---------------------------------------------------------------------------------
+ * finite p  (1 < p < inf)
+ * --------------------------------------------------------------------------------- */
+
+/*
+ * output[b,o,hw] = M * ( sum_i (|input - weight| / M)^p )^(1/p),  M = max_i |input - weight|
+ * (0 when M == 0).  Replaces norm_dist_forward_cuda (model/norm_dist.cpp:7-8, :22-28; kernel
+ * model/norm_dist_cuda.cu:228-292, launcher :427-437).  Agrees with the reference's
+ * arithmetic to 1e-5 relative; it is not bit-identical (the reference itself uses
+ * approximate intrinsics).
+ */
+int linf_norm_dist_forward(const float* input, const float* weight,
+                           int B, int CO, int CI, int G, int HW,
+                           float* output, float p, void* stream);
+
+/*
+ * grad_input[b,i,hw] = sum_o g * (|t| / output)^(p-1) * sign(t), t = input - weight.
+ * Fully overwrites grad_input.  Replaces norm_dist_backward_input_cuda
+ * (model/norm_dist.cpp:9-10, :30-40; kernel model/norm_dist_cuda.cu:299-361, launcher :438-448).
+ */
+int linf_norm_dist_backward_input(const float* grad_output, const float* input,
+                                  const float* weight, const float* output,
+                                  int B, int CO, int CI, int G, int HW,
+                                  float* grad_input, float p, void* stream);
+
+/*
+ * grad_weight[o,i] = sum_{b,hw} g * (|t| / output)^(p-1) * sign(-t).  Fully overwrites
+ * grad_weight with a fixed summation order (no atomics).  Replaces
+ * norm_dist_backward_weight_cuda (model/norm_dist.cpp:11-12, :42-52; kernel
+ * model/norm_dist_cuda.cu:368-425, launcher :449-459).
+ */
+int linf_norm_dist_backward_weight(const float* grad_output, const float* input,
+                                   const float* weight, const float* output,
+                                   int B, int CO, int CI, int G, int HW,
+                                   float* grad_weight, float p, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LINFDIST_H_ */

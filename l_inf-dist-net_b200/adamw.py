@@ -1,0 +1,63 @@
+"""AdamW whose weight decay follows the l_p norm of each weight ROW (semantics of adamw.py:6-86
+of zbh2047/L_inf-dist-net): before the Adam update a row x of a distance layer shrinks along
+the gradient of ||x||_p, i.e. x_i -= lr*wd * (|x_i| / ||x||_p)^(p-2) * x_i; at p = inf only the
+entry of largest magnitude shrinks; parameters of modules without a p shrink uniformly."""
+import math
+
+import torch
+from torch.optim import Optimizer
+
+from .norm_dist import get_p_norm
+
+
+class AdamW(Optimizer):
+    def __init__(self, model, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2):
+        if lr < 0 or eps < 0 or weight_decay < 0:
+            raise ValueError("lr, eps and weight_decay must be non-negative")
+        if not (0 <= betas[0] < 1 and 0 <= betas[1] < 1):
+            raise ValueError("betas must lie in [0, 1)")
+        groups = [{"params": p, "module": m} for m in model.modules() for p in m.parameters(False)]
+        super().__init__(groups, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
+
+    @staticmethod
+    def _decay(p, p_norm, lr_wd, eps):
+        if p_norm is None:
+            p.mul_(1 - lr_wd)
+            return
+        rows = p.view(p.size(0), -1)
+        if math.isinf(p_norm):
+            idx = rows.abs().argmax(dim=1, keepdim=True)
+            rows.scatter_add_(1, idx, -lr_wd * rows.gather(1, idx))
+            return
+        sq = rows * rows + eps
+        sq = sq / sq.amax(dim=1, keepdim=True)
+        pw = sq.pow(p_norm / 2 - 1)
+        scale = (sq * pw).sum(dim=1, keepdim=True).pow(2 / p_norm - 1) * pw
+        p.addcmul_(scale.view_as(p), p, value=-lr_wd)
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        for group in self.param_groups:
+            beta1, beta2 = group["betas"]
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                if p.grad.is_sparse:
+                    raise RuntimeError("AdamW does not support sparse gradients")
+                self._decay(p, get_p_norm(group["module"]), group["lr"] * group["weight_decay"], group["eps"])
+                state = self.state[p]
+                if not state:
+                    state["step"] = 0
+                    state["exp_avg"] = torch.zeros_like(p, memory_format=torch.preserve_format)
+                    state["exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.preserve_format)
+                state["step"] += 1
+                m, v = state["exp_avg"], state["exp_avg_sq"]
+                m.mul_(beta1).add_(p.grad, alpha=1 - beta1)
+                v.mul_(beta2).addcmul_(p.grad, p.grad, value=1 - beta2)
+                denom = (v.sqrt() / math.sqrt(1 - beta2 ** state["step"])).add_(group["eps"])
+                p.addcdiv_(m, denom, value=-group["lr"] / (1 - beta1 ** state["step"]))
+        return loss

@@ -1,0 +1,158 @@
+// extern "C" surface of liblinfdist.so: argument validation, then the launchers.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace linf {
+
+int sm_count() {
+    static int cached[16] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return 148; }
+    if (dev < 0 || dev >= 16) dev = 0;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+            cudaGetLastError();
+            n = 148;
+        }
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+extern int inf_forward_mode;
+extern int inf_forward_bk;
+
+}  // namespace linf
+
+using namespace linf;
+
+namespace {
+inline bool bad_p(float p) { return !(p > 1.f) || isinf(p); }
+inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+}  // namespace
+
+extern "C" {
+
+int linf_version(void) { return 100; }
+
+const char* linf_error_string(int code) {
+    switch (code) {
+        case LINF_OK: return "ok";
+        case LINF_ERR_NULL: return "a required pointer is NULL";
+        case LINF_ERR_DIMS: return "a dimension is not positive or a tensor is too large";
+        case LINF_ERR_GROUP: return "channel counts must be multiples of the group count";
+        case LINF_ERR_P: return "p must be finite and greater than 1";
+        case LINF_ERR_LAUNCH: return "CUDA reported an error at kernel launch";
+        case LINF_ERR_WORKSPACE: return "workspace is missing, misaligned or too small";
+        case LINF_ERR_TOO_LARGE: return "size exceeds a fixed maximum of this entry point";
+        default: return "unknown error code";
+    }
+}
+
+// Process-wide tuning knobs for benchmarking kernel variants ("inf_forward_mode": 0 scalar
+// sub + 2-input max, 1 scalar sub + 3-input max, 2 packed sub + 3-input max; "inf_forward_bk":
+// 16 or 32).  Not part of the drop-in surface; not thread safe.
+int linf_tune_set(int key, int value) {
+    if (key == 0 && value >= 0 && value <= 2) { inf_forward_mode = value; return LINF_OK; }
+    if (key == 1 && (value == 16 || value == 32)) { inf_forward_bk = value; return LINF_OK; }
+    return LINF_ERR_DIMS;
+}
+
+int linf_inf_dist_forward(const float* input, const float* weight, int B, int CO, int CI, int G, int HW,
+                          float* output, int* pos, void* stream) {
+    if (!input || !weight || !output || !pos) return LINF_ERR_NULL;
+    Dims d;
+    int rc = make_dims(B, CO, CI, G, HW, &d);
+    if (rc) return rc;
+    return inf_forward(input, weight, d, output, pos, nullptr, 0, as_stream(stream));
+}
+
+size_t linf_inf_dist_forward_workspace_bytes(int B, int CO, int CI, int G, int HW) {
+    Dims d;
+    if (make_dims(B, CO, CI, G, HW, &d)) return 0;
+    return inf_forward_workspace(d);
+}
+
+int linf_inf_dist_forward_ws(const float* input, const float* weight, int B, int CO, int CI, int G, int HW,
+                             float* output, int* pos, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!input || !weight || !output || !pos) return LINF_ERR_NULL;
+    Dims d;
+    int rc = make_dims(B, CO, CI, G, HW, &d);
+    if (rc) return rc;
+    if (inf_forward_workspace(d) != 0 && workspace == nullptr) return LINF_ERR_WORKSPACE;
+    return inf_forward(input, weight, d, output, pos, workspace, workspace_bytes, as_stream(stream));
+}
+
+int linf_inf_dist_bound_forward(const float* input_lower, const float* input_upper, const float* weight,
+                                int B, int CO, int CI, int G, int HW,
+                                float* output_lower, float* output_upper, void* stream) {
+    if (!input_lower || !input_upper || !weight || !output_lower || !output_upper) return LINF_ERR_NULL;
+    Dims d;
+    int rc = make_dims(B, CO, CI, G, HW, &d);
+    if (rc) return rc;
+    return inf_bound(input_lower, input_upper, weight, d, output_lower, output_upper, as_stream(stream));
+}
+
+int linf_inf_dist_backward_input(const float* grad_output, const int* pos, int B, int CO, int CI, int G, int HW,
+                                 float* grad_input, void* stream) {
+    if (!grad_output || !pos || !grad_input) return LINF_ERR_NULL;
+    Dims d;
+    int rc = make_dims(B, CO, CI, G, HW, &d);
+    if (rc) return rc;
+    return inf_backward_input(grad_output, pos, d, grad_input, as_stream(stream));
+}
+
+int linf_inf_dist_backward_weight(const float* grad_output, const int* pos, int B, int CO, int CI, int G, int HW,
+                                  float* grad_weight, void* stream) {
+    if (!grad_output || !pos || !grad_weight) return LINF_ERR_NULL;
+    Dims d;
+    int rc = make_dims(B, CO, CI, G, HW, &d);
+    if (rc) return rc;
+    return inf_backward_weight(grad_output, pos, d, grad_weight, as_stream(stream));
+}
+
+int linf_inf_dist_backward_atomic(const float* grad_output, const int* pos, int B, int CO, int CI, int G, int HW,
+                                  float* grad_input, float* grad_weight, void* stream) {
+    if (!grad_output || !pos) return LINF_ERR_NULL;
+    if (!grad_input && !grad_weight) return LINF_ERR_NULL;
+    Dims d;
+    int rc = make_dims(B, CO, CI, G, HW, &d);
+    if (rc) return rc;
+    return inf_backward_atomic(grad_output, pos, d, grad_input, grad_weight, as_stream(stream));
+}
+
+int linf_norm_dist_forward(const float* input, const float* weight, int B, int CO, int CI, int G, int HW,
+                           float* output, float p, void* stream) {
+    if (!input || !weight || !output) return LINF_ERR_NULL;
+    if (bad_p(p)) return LINF_ERR_P;
+    Dims d;
+    int rc = make_dims(B, CO, CI, G, HW, &d);
+    if (rc) return rc;
+    return lp_forward(input, weight, d, output, p, as_stream(stream));
+}
+
+int linf_norm_dist_backward_input(const float* grad_output, const float* input, const float* weight,
+                                  const float* output, int B, int CO, int CI, int G, int HW,
+                                  float* grad_input, float p, void* stream) {
+    if (!grad_output || !input || !weight || !output || !grad_input) return LINF_ERR_NULL;
+    if (bad_p(p)) return LINF_ERR_P;
+    Dims d;
+    int rc = make_dims(B, CO, CI, G, HW, &d);
+    if (rc) return rc;
+    return lp_backward_input(grad_output, input, weight, output, d, grad_input, p, as_stream(stream));
+}
+
+int linf_norm_dist_backward_weight(const float* grad_output, const float* input, const float* weight,
+                                   const float* output, int B, int CO, int CI, int G, int HW,
+                                   float* grad_weight, float p, void* stream) {
+    if (!grad_output || !input || !weight || !output || !grad_weight) return LINF_ERR_NULL;
+    if (bad_p(p)) return LINF_ERR_P;
+    Dims d;
+    int rc = make_dims(B, CO, CI, G, HW, &d);
+    if (rc) return rc;
+    return lp_backward_weight(grad_output, input, weight, output, d, grad_weight, p, as_stream(stream));
+}
+
+}  // extern "C"

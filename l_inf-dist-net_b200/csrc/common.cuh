@@ -1,0 +1,93 @@
+// Shared declarations of the distance-neuron kernels (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stddef.h>
+
+#include "../../include/linfdist.h"
+
+namespace linf {
+
+// Problem sizes of one call.  R = B*HW is the number of "rows" (one per batch element and
+// spatial position); per group the work is an R x COg x CIg reduction over CIg.
+struct Dims {
+    int B, CO, CI, G, HW;
+    int COg, CIg;   // per-group channel counts
+    int R;          // B * HW
+};
+
+// Validates sizes; fills d.  Every product that is later used as an element count has to
+// fit in int32 (the tensors of a layer are far below that).
+inline int make_dims(int B, int CO, int CI, int G, int HW, Dims* d) {
+    if (B <= 0 || CO <= 0 || CI <= 0 || G <= 0 || HW <= 0) return LINF_ERR_DIMS;
+    if (CI % G != 0 || CO % G != 0) return LINF_ERR_GROUP;
+    const long long lim = 0x7fffffffLL;
+    if ((long long)B * HW > lim || (long long)B * HW * CO > lim ||
+        (long long)B * HW * CI > lim || (long long)CO * (CI / G) > lim)
+        return LINF_ERR_DIMS;
+    d->B = B; d->CO = CO; d->CI = CI; d->G = G; d->HW = HW;
+    d->COg = CO / G; d->CIg = CI / G; d->R = B * HW;
+    return LINF_OK;
+}
+
+inline int launch_status() {
+    return cudaGetLastError() == cudaSuccess ? LINF_OK : LINF_ERR_LAUNCH;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Number of SMs of the current device (cached per device id; read-only after first use).
+int sm_count();
+
+// ---- element addressing ------------------------------------------------------------
+// row r = b*HW + hw of group g, channel c of that group, in a [B, C, HW] tensor whose
+// per-group channel count is Cg.
+__device__ __forceinline__ size_t act_index(int r, int g, int c, int Cg, int G, int HW) {
+    int b = r / HW, hw = r - b * HW;
+    return ((size_t)(b * G + g) * Cg + c) * HW + hw;
+}
+
+// ---- Blackwell packed / 3-input fp32 instructions ------------------------------------
+// Two IEEE round-to-nearest fp32 subtractions in one instruction (no flush-to-zero).
+__device__ __forceinline__ unsigned long long sub_f32x2(unsigned long long a, unsigned long long b) {
+    unsigned long long r;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack_f32x2(unsigned long long v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+// max(a, b, c) in one instruction; a NaN operand is ignored (same rule as fmaxf).
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
+// ---- cp.async (16-byte, L2-only caching) ----------------------------------------------
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, int src_bytes) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+
+// ---- launchers implemented in the .cu files -----------------------------------------
+int inf_forward(const float* x, const float* w, const Dims& d, float* y, int* pos,
+                void* ws, size_t ws_bytes, cudaStream_t st);
+size_t inf_forward_workspace(const Dims& d);
+int inf_bound(const float* xl, const float* xu, const float* w, const Dims& d,
+              float* yl, float* yu, cudaStream_t st);
+int inf_backward_input(const float* g, const int* pos, const Dims& d, float* gx, cudaStream_t st);
+int inf_backward_weight(const float* g, const int* pos, const Dims& d, float* gw, cudaStream_t st);
+int inf_backward_atomic(const float* g, const int* pos, const Dims& d, float* gx, float* gw,
+                        cudaStream_t st);
+int lp_forward(const float* x, const float* w, const Dims& d, float* y, float p, cudaStream_t st);
+int lp_backward_input(const float* g, const float* x, const float* w, const float* y,
+                      const Dims& d, float* gx, float p, cudaStream_t st);
+int lp_backward_weight(const float* g, const float* x, const float* w, const float* y,
+                       const Dims& d, float* gw, float p, cudaStream_t st);
+
+}  // namespace linf

@@ -1,0 +1,483 @@
+// inf-dist forward: y[r,o] = max_i |x[r,i] - w[o,i]| with capture of the lowest arg-max index.
+//
+// Two paths:
+//   * tiled path (dense layers: HW == 1, CI/G a multiple of 4, 16-byte aligned pointers):
+//     a register-tiled (max, |a-b|) "GEMM" on the FP32 cores.  A CTA of 128 threads owns a
+//     64 x 128 output tile, a thread an 8 x 8 sub-tile.  Operand tiles are staged through
+//     shared memory with cp.async in a multi-stage ring and read back with 128-bit loads
+//     along k, so that two neighbouring k-terms of one output sit in one 64-bit register
+//     pair: one packed `sub.f32x2` produces both differences and one 3-input `max.f32`
+//     folds both |differences| into the running maximum (one issue slot per term).
+//     The arg-max is NOT tracked per term.  The loop only records, once per k-tile, which
+//     k-tile last raised the maximum; after the loop the winning k-tile alone is rescanned
+//     for the first index whose |difference| equals the maximum (strict ">" between tiles
+//     plus first-match inside a tile = lowest index among exact ties).
+//     With scratch memory the k-tiles of all output tiles are dealt out evenly to
+//     2 CTAs per SM; an output tile cut by a CTA boundary is finished by whichever of its
+//     CTAs arrives last (ticket counter, nobody waits).
+//   * generic path (any G, HW, alignment): 32 x 32 tile, index tracked per term.
+#include "common.cuh"
+
+namespace linf {
+
+// =====================================================================================
+// generic path
+// =====================================================================================
+namespace {
+
+constexpr int GT = 32;  // generic tile edge
+
+template <bool ROW_FAST>
+__global__ void __launch_bounds__(256)
+inf_forward_generic_kernel(const float* __restrict__ x, const float* __restrict__ w, Dims d,
+                           float* __restrict__ y, int* __restrict__ pos) {
+    __shared__ float xs[GT][GT + 1];  // [k][row]
+    __shared__ float ws[GT][GT + 1];  // [k][col]
+    const int tid = threadIdx.x, tx = tid & 31, ty = tid >> 5;
+    const int g = blockIdx.z, r0 = blockIdx.x * GT, c0 = blockIdx.y * GT;
+
+    float best[4] = {0.f, 0.f, 0.f, 0.f};
+    int arg[4] = {0, 0, 0, 0};
+
+    for (int k0 = 0; k0 < d.CIg; k0 += GT) {
+        for (int e = tid; e < GT * GT; e += 256) {
+            int kl, rl;
+            if (ROW_FAST) { rl = e & 31; kl = e >> 5; } else { kl = e & 31; rl = e >> 5; }
+            int r = r0 + rl, k = k0 + kl;
+            xs[kl][rl] = (r < d.R && k < d.CIg) ? x[act_index(r, g, k, d.CIg, d.G, d.HW)] : 0.f;
+            int kw = e & 31, cl = e >> 5, c = c0 + cl, k2 = k0 + kw;
+            ws[kw][cl] = (c < d.COg && k2 < d.CIg) ? w[(size_t)(g * d.COg + c) * d.CIg + k2] : 0.f;
+        }
+        __syncthreads();
+        const int kmax = min(GT, d.CIg - k0);
+        for (int kk = 0; kk < kmax; ++kk) {
+            const float wv = ws[kk][tx];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float t = xs[kk][ty + 8 * j] - wv;
+                float a = fabsf(t);
+                if (a > best[j]) {
+                    best[j] = a;
+                    arg[j] = (k0 + kk) | (t >= 0.f ? 0 : (int)0x80000000);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    const int c = c0 + tx;
+    if (c < d.COg) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            int r = r0 + ty + 8 * j;
+            if (r < d.R) {
+                size_t o = act_index(r, g, c, d.COg, d.G, d.HW);
+                y[o] = best[j];
+                if (pos) pos[o] = arg[j];
+            }
+        }
+    }
+}
+
+// =====================================================================================
+// tiled path
+// =====================================================================================
+constexpr int BM = 64, BN = 128, NT = 128;   // CTA tile and thread count
+constexpr int TILE_OUT = BM * BN;            // outputs per tile (64 per thread)
+
+template <int BK>
+struct TileCfg {
+    static constexpr int LD = BK + 4;                 // padded row length in floats
+    static constexpr int STAGES = (BK == 16) ? 4 : 3;
+    static constexpr int STAGE_FLOATS = (BM + BN) * LD;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_FLOATS * 4;
+};
+
+struct TiledParams {
+    const float* x; const float* w; float* y; int* pos;
+    int M, N, K, G;        // rows, per-group outputs, per-group inputs, groups
+    int lda;               // floats between consecutive rows of x (= CI)
+    int ldo;               // floats between consecutive rows of y (= CO)
+    int tiles_m, tiles_n;  // per group
+    int KT;                // k-tiles per output tile
+    int n_cta;             // CTAs of the launch (units are dealt evenly to them)
+    int* tickets;          // one counter per output tile (split mode), else nullptr
+    float* part_val;       // [n_cta][2][TILE_OUT]
+    int* part_cid;         // [n_cta][2][TILE_OUT]
+};
+
+__device__ __forceinline__ long long unit_begin(const TiledParams& p, int c) {
+    long long total = (long long)p.tiles_m * p.tiles_n * p.G * p.KT;
+    return total * c / p.n_cta;
+}
+
+template <int BK>
+__device__ __forceinline__ void load_stage(float* stage, const TiledParams& p, int g, int m0, int n0,
+                                           int kt, int tid) {
+    using C = TileCfg<BK>;
+    constexpr int CH = BK / 4;  // 16-byte chunks per row
+    const int k0 = kt * BK;
+    float* As = stage;
+    float* Bs = stage + BM * C::LD;
+#pragma unroll
+    for (int q = tid; q < BM * CH; q += NT) {
+        int row = q / CH, ch = q % CH;
+        int m = min(m0 + row, p.M - 1);
+        int k = k0 + ch * 4;
+        bool in = k < p.K;
+        const float* src = p.x + (size_t)m * p.lda + (size_t)g * p.K + (in ? k : 0);
+        cp_async16(As + row * C::LD + ch * 4, src, in ? 16 : 0);
+    }
+#pragma unroll
+    for (int q = tid; q < BN * CH; q += NT) {
+        int row = q / CH, ch = q % CH;
+        int n = min(n0 + row, p.N - 1);
+        int k = k0 + ch * 4;
+        bool in = k < p.K;
+        const float* src = p.w + ((size_t)g * p.N + n) * p.K + (in ? k : 0);
+        cp_async16(Bs + row * C::LD + ch * 4, src, in ? 16 : 0);
+    }
+}
+
+// One k-tile of the (max, |a-b|) product for the 8 x 8 sub-tile of this thread.
+// `in` holds the running maxima before the tile, `out` after it (they may alias).
+template <int BK, int MODE>
+__device__ __forceinline__ void tile_step(const float* __restrict__ As, const float* __restrict__ Bs,
+                                          const float (&in)[64], float (&out)[64]) {
+    constexpr int LD = TileCfg<BK>::LD;
+#pragma unroll
+    for (int k4 = 0; k4 < BK / 4; ++k4) {
+        ulonglong2 bf[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            bf[j] = *reinterpret_cast<const ulonglong2*>(Bs + (8 * j) * LD + k4 * 4);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const ulonglong2 af = *reinterpret_cast<const ulonglong2*>(As + (4 * i) * LD + k4 * 4);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float a = (k4 == 0) ? in[i * 8 + j] : out[i * 8 + j];
+                float t0, t1, t2, t3;
+                if (MODE == 2) {
+                    unpack_f32x2(sub_f32x2(af.x, bf[j].x), t0, t1);
+                    unpack_f32x2(sub_f32x2(af.y, bf[j].y), t2, t3);
+                } else {
+                    float a0, a1, a2, a3, b0, b1, b2, b3;
+                    unpack_f32x2(af.x, a0, a1); unpack_f32x2(af.y, a2, a3);
+                    unpack_f32x2(bf[j].x, b0, b1); unpack_f32x2(bf[j].y, b2, b3);
+                    t0 = a0 - b0; t1 = a1 - b1; t2 = a2 - b2; t3 = a3 - b3;
+                }
+                if (MODE >= 1) {
+                    a = max3(a, fabsf(t0), fabsf(t1));
+                    a = max3(a, fabsf(t2), fabsf(t3));
+                } else {
+                    a = fmaxf(a, fabsf(t0)); a = fmaxf(a, fabsf(t1));
+                    a = fmaxf(a, fabsf(t2)); a = fmaxf(a, fabsf(t3));
+                }
+                out[i * 8 + j] = a;
+            }
+        }
+    }
+}
+
+// After a k-tile: every output whose maximum rose remembers the tile number.  Two 16-bit
+// tile numbers share a register; `ktdup` holds the tile number in both halves.
+__device__ __forceinline__ void note_raises(const float (&before)[64], const float (&after)[64],
+                                            unsigned (&cid)[32], unsigned ktdup) {
+#pragma unroll
+    for (int e = 0; e < 64; e += 2) {
+        if (after[e] > before[e]) cid[e >> 1] = __byte_perm(cid[e >> 1], ktdup, 0x3254);
+        if (after[e + 1] > before[e + 1]) cid[e >> 1] = __byte_perm(cid[e >> 1], ktdup, 0x7610);
+    }
+}
+
+__device__ __forceinline__ void cid_set(unsigned (&cid)[32], int e, unsigned v) {
+    v &= 0xffffu;
+    cid[e >> 1] = (e & 1) ? ((cid[e >> 1] & 0x0000ffffu) | (v << 16)) : ((cid[e >> 1] & 0xffff0000u) | v);
+}
+
+__device__ __forceinline__ int cid_get(const unsigned (&cid)[32], int e) {
+    return (e & 1) ? (int)(cid[e >> 1] >> 16) : (int)(cid[e >> 1] & 0xffffu);
+}
+
+// Finds the first index in k-tile `kt` whose |x - w| equals yv, and the sign there.
+template <int BK>
+__device__ __forceinline__ int resolve_pos(const float* __restrict__ xrow, const float* __restrict__ wrow,
+                                           int kt, int K, float yv) {
+    if (!(yv > 0.f)) return 0;
+    const int kbase = kt * BK;
+    int best = 0;
+    float tb = 0.f;
+#pragma unroll
+    for (int q = BK / 4 - 1; q >= 0; --q) {
+        if (kbase + 4 * q < K) {
+            const float4 xv = __ldg(reinterpret_cast<const float4*>(xrow + kbase + 4 * q));
+            const float4 wv = __ldg(reinterpret_cast<const float4*>(wrow + kbase + 4 * q));
+            float t;
+            t = xv.w - wv.w; if (fabsf(t) == yv) { best = 4 * q + 3; tb = t; }
+            t = xv.z - wv.z; if (fabsf(t) == yv) { best = 4 * q + 2; tb = t; }
+            t = xv.y - wv.y; if (fabsf(t) == yv) { best = 4 * q + 1; tb = t; }
+            t = xv.x - wv.x; if (fabsf(t) == yv) { best = 4 * q + 0; tb = t; }
+        }
+    }
+    return (kbase + best) | (tb < 0.f ? (int)0x80000000 : 0);
+}
+
+template <int BK, int MODE, bool TRACK>
+__global__ void __launch_bounds__(NT, 2)
+inf_forward_tiled_kernel(const TiledParams p) {
+    using C = TileCfg<BK>;
+    extern __shared__ __align__(16) float smem[];
+    __shared__ int s_last;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int wm = warp & 1, wn = warp >> 1, lm = lane >> 3, ln = lane & 7;
+    const int row_off = wm * 32 + lm;   // + 4*i
+    const int col_off = wn * 64 + ln;   // + 8*j
+
+    const int tiles_per_group = p.tiles_m * p.tiles_n;
+    long long u = unit_begin(p, blockIdx.x);
+    const long long u_end = unit_begin(p, blockIdx.x + 1);
+    int seg = 0;
+
+    while (u < u_end) {
+        const int tile = (int)(u / p.KT);
+        const int kt0 = (int)(u - (long long)tile * p.KT);
+        const int kt1 = (int)min((long long)p.KT, kt0 + (u_end - u));
+        const int g = tile / tiles_per_group;
+        const int tg = tile - g * tiles_per_group;
+        const int n0 = (tg / p.tiles_m) * BN, m0 = (tg % p.tiles_m) * BM;
+
+        float accA[64];
+        float accB[TRACK ? 64 : 1];
+        unsigned cid[TRACK ? 32 : 1];
+#pragma unroll
+        for (int e = 0; e < 64; ++e) accA[e] = 0.f;
+        if (TRACK) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) cid[e] = (unsigned)kt0 * 0x10001u;
+        }
+
+        // ---- software pipeline over the k-tiles of this segment ----
+        __syncthreads();   // previous segment is done with the ring
+#pragma unroll
+        for (int s = 0; s < C::STAGES - 1; ++s) {
+            if (kt0 + s < kt1) load_stage<BK>(smem + s * C::STAGE_FLOATS, p, g, m0, n0, kt0 + s, tid);
+            cp_async_commit();
+        }
+        int rd = 0, wr = C::STAGES - 1;
+        for (int kt = kt0; kt < kt1; kt += 2) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int ktc = kt + h;
+                if (ktc < kt1) {
+                    cp_async_wait<C::STAGES - 2>();
+                    __syncthreads();
+                    if (ktc + C::STAGES - 1 < kt1)
+                        load_stage<BK>(smem + wr * C::STAGE_FLOATS, p, g, m0, n0, ktc + C::STAGES - 1, tid);
+                    cp_async_commit();
+                    const float* As = smem + rd * C::STAGE_FLOATS + row_off * C::LD;
+                    const float* Bs = smem + rd * C::STAGE_FLOATS + (BM + col_off) * C::LD;
+                    if (TRACK) {
+                        if (h == 0) {
+                            tile_step<BK, MODE>(As, Bs, accA, reinterpret_cast<float(&)[64]>(accB));
+                            note_raises(accA, reinterpret_cast<float(&)[64]>(accB),
+                                        reinterpret_cast<unsigned(&)[32]>(cid), (unsigned)ktc * 0x10001u);
+                        } else {
+                            tile_step<BK, MODE>(As, Bs, reinterpret_cast<float(&)[64]>(accB), accA);
+                            note_raises(reinterpret_cast<float(&)[64]>(accB), accA,
+                                        reinterpret_cast<unsigned(&)[32]>(cid), (unsigned)ktc * 0x10001u);
+                        }
+                    } else {
+                        tile_step<BK, MODE>(As, Bs, accA, accA);
+                    }
+                    rd = (rd + 1 == C::STAGES) ? 0 : rd + 1;
+                    wr = (wr + 1 == C::STAGES) ? 0 : wr + 1;
+                } else if (TRACK && h == 1) {
+                    // odd number of k-tiles: the result sits in accB
+#pragma unroll
+                    for (int e = 0; e < 64; ++e) accA[e] = reinterpret_cast<float(&)[64]>(accB)[e];
+                }
+            }
+        }
+        cp_async_wait<0>();
+
+        // ---- finish the segment ----
+        const bool complete = (kt0 == 0 && kt1 == p.KT);
+        bool finish = complete;
+        if (!complete) {
+            // park the partial result, then take a ticket: the last arrival merges
+            const size_t slot = ((size_t)blockIdx.x * 2 + (seg ? 1 : 0)) * TILE_OUT;
+#pragma unroll
+            for (int e = 0; e < 64; ++e) {
+                p.part_val[slot + e * NT + tid] = accA[e];
+                if (TRACK) p.part_cid[slot + e * NT + tid] = cid_get(reinterpret_cast<unsigned(&)[32]>(cid), e);
+            }
+            __threadfence();
+            __syncthreads();
+            // CTAs that share this tile: consecutive block ids
+            const long long t_begin = (long long)tile * p.KT, t_end = t_begin + p.KT;
+            int c_lo = blockIdx.x, c_hi = blockIdx.x;
+            while (c_lo > 0 && unit_begin(p, c_lo) > t_begin) --c_lo;
+            while (c_hi + 1 < p.n_cta && unit_begin(p, c_hi + 1) < t_end) ++c_hi;
+            if (tid == 0) {
+                int old = atomicAdd(&p.tickets[tile], 1);
+                int last = (old == c_hi - c_lo);
+                if (last) p.tickets[tile] = 0;   // leave the counter clean for the next call
+                s_last = last;
+            }
+            __syncthreads();
+            if (s_last) {
+                __threadfence();
+                // Merge the parked partial results of the other CTAs of this tile into the
+                // registers.  A partial from an EARLIER k-range wins ties (lowest index rule),
+                // one from a LATER k-range must be strictly larger.
+                for (int c = (int)blockIdx.x - 1; c >= c_lo; --c) {
+                    const int s2 = ((int)(unit_begin(p, c) / p.KT) == tile) ? 0 : 1;
+                    const size_t sl = ((size_t)c * 2 + s2) * TILE_OUT;
+#pragma unroll
+                    for (int e = 0; e < 64; ++e) {
+                        const float v = __ldcg(p.part_val + sl + e * NT + tid);
+                        if (v >= accA[e]) {
+                            accA[e] = v;
+                            if (TRACK) cid_set(reinterpret_cast<unsigned(&)[32]>(cid), e,
+                                               (unsigned)__ldcg(p.part_cid + sl + e * NT + tid));
+                        }
+                    }
+                }
+                for (int c = (int)blockIdx.x + 1; c <= c_hi; ++c) {
+                    const size_t sl = ((size_t)c * 2 + 0) * TILE_OUT;   // always that CTA's first segment
+#pragma unroll
+                    for (int e = 0; e < 64; ++e) {
+                        const float v = __ldcg(p.part_val + sl + e * NT + tid);
+                        if (v > accA[e]) {
+                            accA[e] = v;
+                            if (TRACK) cid_set(reinterpret_cast<unsigned(&)[32]>(cid), e,
+                                               (unsigned)__ldcg(p.part_cid + sl + e * NT + tid));
+                        }
+                    }
+                }
+                finish = true;
+            }
+        }
+        if (finish) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int m = m0 + row_off + 4 * i;
+                if (m < p.M) {
+                    const float* xrow = p.x + (size_t)m * p.lda + (size_t)g * p.K;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int n = n0 + col_off + 8 * j;
+                        if (n < p.N) {
+                            const float yv = accA[i * 8 + j];
+                            const size_t o = (size_t)m * p.ldo + (size_t)g * p.N + n;
+                            p.y[o] = yv;
+                            if (TRACK) {
+                                const float* wrow = p.w + ((size_t)g * p.N + n) * p.K;
+                                p.pos[o] = resolve_pos<BK>(
+                                    xrow, wrow, cid_get(reinterpret_cast<unsigned(&)[32]>(cid), i * 8 + j),
+                                    p.K, yv);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        u += kt1 - kt0;
+        ++seg;   // only the first and the last segment of a CTA can be partial
+    }
+}
+
+template <int BK, int MODE, bool TRACK>
+int launch_tiled(const TiledParams& p, cudaStream_t st) {
+    using C = TileCfg<BK>;
+    auto kern = inf_forward_tiled_kernel<BK, MODE, TRACK>;
+    static bool configured[16] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 16 && !configured[dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
+            return LINF_ERR_LAUNCH;
+        configured[dev] = true;
+    }
+    kern<<<p.n_cta, NT, C::SMEM_BYTES, st>>>(p);
+    return launch_status();
+}
+
+size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+}  // namespace
+
+// Shapes the tiled path accepts.
+static bool tiled_ok(const float* x, const float* w, const Dims& d) {
+    return d.HW == 1 && (d.CIg % 4) == 0 && aligned16(x) && aligned16(w) &&
+           d.COg >= 32 && (d.CIg + 15) / 16 < 65536;
+}
+
+static int tiled_tiles(const Dims& d) {
+    return ((d.R + BM - 1) / BM) * ((d.COg + BN - 1) / BN) * d.G;
+}
+
+// Splitting k-tiles across CTAs pays when whole tiles would leave a large part of the last
+// wave of CTAs idle.
+static bool want_split(const Dims& d) {
+    const int slots = 2 * sm_count();
+    const int tiles = tiled_tiles(d);
+    const int waves = (tiles + slots - 1) / slots;
+    return (double)tiles / ((double)waves * slots) < 0.9;
+}
+
+size_t inf_forward_workspace(const Dims& d) {
+    if (d.HW != 1 || (d.CIg % 4) != 0 || d.COg < 32) return 0;
+    if (!want_split(d)) return 0;
+    const size_t n_cta = 2 * (size_t)sm_count();
+    return align256((size_t)tiled_tiles(d) * sizeof(int)) + n_cta * 2 * TILE_OUT * (sizeof(float) + sizeof(int));
+}
+
+int inf_forward_mode = 2;   // instruction variant of the tiled kernel (2 = packed sub + 3-input max)
+int inf_forward_bk = 16;
+
+int inf_forward(const float* x, const float* w, const Dims& d, float* y, int* pos,
+                void* ws, size_t ws_bytes, cudaStream_t st) {
+    if (!tiled_ok(x, w, d)) {
+        dim3 grid((d.R + GT - 1) / GT, (d.COg + GT - 1) / GT, d.G);
+        if (grid.y > 65535u || grid.z > 65535u) return LINF_ERR_DIMS;
+        if (d.HW > 1) inf_forward_generic_kernel<true><<<grid, 256, 0, st>>>(x, w, d, y, pos);
+        else inf_forward_generic_kernel<false><<<grid, 256, 0, st>>>(x, w, d, y, pos);
+        return launch_status();
+    }
+    TiledParams p;
+    p.x = x; p.w = w; p.y = y; p.pos = pos;
+    p.M = d.R; p.N = d.COg; p.K = d.CIg; p.G = d.G;
+    p.lda = d.CI; p.ldo = d.CO;
+    p.tiles_m = (d.R + BM - 1) / BM; p.tiles_n = (d.COg + BN - 1) / BN;
+    const int BK = inf_forward_bk;
+    p.KT = (d.CIg + BK - 1) / BK;
+    const int tiles = p.tiles_m * p.tiles_n * d.G;
+    p.tickets = nullptr; p.part_val = nullptr; p.part_cid = nullptr;
+    p.n_cta = tiles;
+    const size_t need = inf_forward_workspace(d);
+    if (ws != nullptr && need != 0 && want_split(d)) {
+        if (ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 255u)) return LINF_ERR_WORKSPACE;
+        const size_t tick_bytes = align256((size_t)tiles * sizeof(int));
+        long long total = (long long)tiles * p.KT;
+        p.n_cta = (int)min((long long)2 * sm_count(), total);
+        p.tickets = reinterpret_cast<int*>(ws);
+        p.part_val = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + tick_bytes);
+        p.part_cid = reinterpret_cast<int*>(p.part_val + (size_t)2 * sm_count() * 2 * TILE_OUT);
+        if (cudaMemsetAsync(p.tickets, 0, tick_bytes, st) != cudaSuccess) return LINF_ERR_LAUNCH;
+    }
+    const int mode = inf_forward_mode;
+    const bool track = pos != nullptr;
+#define LINF_DISPATCH(BKV, MODEV)                                                     \
+    if (BK == BKV && mode == MODEV)                                                   \
+        return track ? launch_tiled<BKV, MODEV, true>(p, st) : launch_tiled<BKV, MODEV, false>(p, st);
+    LINF_DISPATCH(16, 2)
+    LINF_DISPATCH(16, 1)
+    LINF_DISPATCH(16, 0)
+    LINF_DISPATCH(32, 2)
+#undef LINF_DISPATCH
+    return LINF_ERR_LAUNCH;
+}
+
+}  // namespace linf

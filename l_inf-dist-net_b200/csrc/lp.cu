@@ -1,0 +1,248 @@
+// L_p-distance neuron for finite p > 1.
+//
+//   forward   y = M * (sum_i (|x_i - w_i| / M)^p)^(1/p),  M = max_i |x_i - w_i|
+//   backward  T[r,o,i] = g[r,o] * (|t| / y[r,o])^(p-1) * sign(t),  t = x[r,i] - w[o,i]
+//             grad_x[r,i] = sum_o T,   grad_w[o,i] = -sum_r T
+//
+// Powers.  Every base u = |t| / M (or |t| / y) lies in [0, 1].  The exponent q is split as
+// q = n + f with integer n and 0 <= f < 1: u^n comes from square-and-multiply on the FP32
+// pipe (the loop is uniform: q is a launch constant), u^f from one log2/exp2 pair on the
+// special-function unit and only when f != 0.  The approximation error of log2 is thereby
+// multiplied by f < 1 instead of by q, which keeps the gradients of p = 64 ... 1000 within a
+// few ulp of correctly rounded arithmetic; integer p (the common test points 8, 16, 64) never
+// touches the special-function unit at all.
+//
+// Forward normalisation.  M is produced first by the inf-dist forward kernel (value-only mode)
+// straight into `output`; the power-sum kernel reads it from there and overwrites it with y.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace linf {
+namespace {
+
+struct PowPlan {
+    int n;      // integer part of the exponent
+    float f;    // fractional part, 0 <= f < 1
+};
+
+inline PowPlan make_plan(float q) {
+    PowPlan pl;
+    float fl = floorf(q);
+    pl.n = (int)fl;
+    pl.f = q - fl;
+    return pl;
+}
+
+// u^(n+f) for 0 <= u <= 1 (u = 0 gives 0 because n >= 1 on every path that calls this).
+__device__ __forceinline__ float pow_unit(float u, const PowPlan pl) {
+    float r = 1.f, b = u;
+    for (int n = pl.n; n != 0; n >>= 1) {
+        if (n & 1) r *= b;
+        b *= b;
+    }
+    if (pl.f != 0.f) r *= exp2f(pl.f * __log2f(u));   // u = 0: exp2(-inf) = 0
+    return r;
+}
+
+constexpr int GT = 32;
+
+// ---- forward: y holds M on entry, the L_p distance on exit ---------------------------------
+template <bool ROW_FAST>
+__global__ void __launch_bounds__(256)
+lp_forward_generic_kernel(const float* __restrict__ x, const float* __restrict__ w, Dims d,
+                          float* __restrict__ y, PowPlan pl, float inv_p) {
+    __shared__ float xs[GT][GT + 1], ws[GT][GT + 1];
+    const int tid = threadIdx.x, tx = tid & 31, ty = tid >> 5;
+    const int g = blockIdx.z, r0 = blockIdx.x * GT, c0 = blockIdx.y * GT;
+    const int c = c0 + tx;
+
+    float M[4], rM[4], S[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        int r = r0 + ty + 8 * j;
+        M[j] = (r < d.R && c < d.COg) ? y[act_index(r, g, c, d.COg, d.G, d.HW)] : 0.f;
+        rM[j] = M[j] > 0.f ? 1.f / M[j] : 0.f;
+        S[j] = 0.f;
+    }
+    for (int k0 = 0; k0 < d.CIg; k0 += GT) {
+        for (int e = tid; e < GT * GT; e += 256) {
+            int kl, rl;
+            if (ROW_FAST) { rl = e & 31; kl = e >> 5; } else { kl = e & 31; rl = e >> 5; }
+            int r = r0 + rl, k = k0 + kl;
+            xs[kl][rl] = (r < d.R && k < d.CIg) ? x[act_index(r, g, k, d.CIg, d.G, d.HW)] : 0.f;
+            int kw = e & 31, cl = e >> 5, cc = c0 + cl, k2 = k0 + kw;
+            ws[kw][cl] = (cc < d.COg && k2 < d.CIg) ? w[(size_t)(g * d.COg + cc) * d.CIg + k2] : 0.f;
+        }
+        __syncthreads();
+        const int kmax = min(GT, d.CIg - k0);
+        for (int kk = 0; kk < kmax; ++kk) {
+            const float wv = ws[kk][tx];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float u = fminf(fabsf(xs[kk][ty + 8 * j] - wv) * rM[j], 1.f);
+                S[j] += pow_unit(u, pl);
+            }
+        }
+        __syncthreads();
+    }
+    if (c < d.COg) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            int r = r0 + ty + 8 * j;
+            if (r < d.R) y[act_index(r, g, c, d.COg, d.G, d.HW)] = M[j] > 0.f ? powf(S[j], inv_p) * M[j] : 0.f;
+        }
+    }
+}
+
+// ---- backward w.r.t. the input: tile = 32 rows x 32 input channels, loop over outputs -------
+template <bool ROW_FAST>
+__global__ void __launch_bounds__(256)
+lp_backward_input_generic_kernel(const float* __restrict__ gout, const float* __restrict__ x,
+                                 const float* __restrict__ w, const float* __restrict__ y, Dims d,
+                                 float* __restrict__ gx, PowPlan pl) {
+    __shared__ float gs[GT][GT + 1], ys[GT][GT + 1], ws[GT][GT + 1];   // [o][row], [o][row], [o][i]
+    const int tid = threadIdx.x, tx = tid & 31, ty = tid >> 5;
+    const int g = blockIdx.z, r0 = blockIdx.x * GT, i0 = blockIdx.y * GT;
+    const int i = i0 + tx;
+
+    float xv[4], acc[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        int r = r0 + ty + 8 * j;
+        xv[j] = (r < d.R && i < d.CIg) ? x[act_index(r, g, i, d.CIg, d.G, d.HW)] : 0.f;
+        acc[j] = 0.f;
+    }
+    for (int o0 = 0; o0 < d.COg; o0 += GT) {
+        for (int e = tid; e < GT * GT; e += 256) {
+            int ol, rl;
+            if (ROW_FAST) { rl = e & 31; ol = e >> 5; } else { ol = e & 31; rl = e >> 5; }
+            int r = r0 + rl, o = o0 + ol;
+            bool in = r < d.R && o < d.COg;
+            size_t a = in ? act_index(r, g, o, d.COg, d.G, d.HW) : 0;
+            float yv = in ? y[a] : 0.f;
+            gs[ol][rl] = in ? gout[a] : 0.f;
+            ys[ol][rl] = yv > 0.f ? 1.f / yv : 0.f;
+            int il = e & 31, ow = e >> 5, ii = i0 + il, oo = o0 + ow;
+            ws[ow][il] = (ii < d.CIg && oo < d.COg) ? w[(size_t)(g * d.COg + oo) * d.CIg + ii] : 0.f;
+        }
+        __syncthreads();
+        const int omax = min(GT, d.COg - o0);
+        for (int oo = 0; oo < omax; ++oo) {
+            const float wv = ws[oo][tx];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float t = xv[j] - wv;
+                float u = fminf(fabsf(t) * ys[oo][ty + 8 * j], 1.f);
+                float term = gs[oo][ty + 8 * j] * pow_unit(u, pl);
+                acc[j] += (t > 0.f) ? term : -term;
+            }
+        }
+        __syncthreads();
+    }
+    if (i < d.CIg) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            int r = r0 + ty + 8 * j;
+            if (r < d.R) gx[act_index(r, g, i, d.CIg, d.G, d.HW)] = acc[j];
+        }
+    }
+}
+
+// ---- backward w.r.t. the weight: tile = 32 outputs x 32 input channels, loop over rows ------
+template <bool ROW_FAST>
+__global__ void __launch_bounds__(256)
+lp_backward_weight_generic_kernel(const float* __restrict__ gout, const float* __restrict__ x,
+                                  const float* __restrict__ w, const float* __restrict__ y, Dims d,
+                                  float* __restrict__ gw, PowPlan pl) {
+    __shared__ float gs[GT][GT + 1], ys[GT][GT + 1], xs[GT][GT + 1];   // [row][o], [row][o], [row][i]
+    const int tid = threadIdx.x, tx = tid & 31, ty = tid >> 5;
+    const int g = blockIdx.z, o0 = blockIdx.x * GT, i0 = blockIdx.y * GT;
+    const int i = i0 + tx;
+
+    float wv[4], acc[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        int o = o0 + ty + 8 * j;
+        wv[j] = (o < d.COg && i < d.CIg) ? w[(size_t)(g * d.COg + o) * d.CIg + i] : 0.f;
+        acc[j] = 0.f;
+    }
+    for (int rb = 0; rb < d.R; rb += GT) {
+        for (int e = tid; e < GT * GT; e += 256) {
+            {   // grad_output / output tile [row][o]
+                int ol, rl;
+                if (ROW_FAST) { rl = e & 31; ol = e >> 5; } else { ol = e & 31; rl = e >> 5; }
+                int r = rb + rl, o = o0 + ol;
+                bool in = r < d.R && o < d.COg;
+                size_t a = in ? act_index(r, g, o, d.COg, d.G, d.HW) : 0;
+                float yv = in ? y[a] : 0.f;
+                gs[rl][ol] = in ? gout[a] : 0.f;
+                ys[rl][ol] = yv > 0.f ? 1.f / yv : 0.f;
+            }
+            {   // input tile [row][i]
+                int il, rl;
+                if (ROW_FAST) { rl = e & 31; il = e >> 5; } else { il = e & 31; rl = e >> 5; }
+                int r = rb + rl, ii = i0 + il;
+                xs[rl][il] = (r < d.R && ii < d.CIg) ? x[act_index(r, g, ii, d.CIg, d.G, d.HW)] : 0.f;
+            }
+        }
+        __syncthreads();
+        const int rmax = min(GT, d.R - rb);
+        for (int rr = 0; rr < rmax; ++rr) {
+            const float xvv = xs[rr][tx];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float t = wv[j] - xvv;
+                float u = fminf(fabsf(t) * ys[rr][ty + 8 * j], 1.f);
+                float term = gs[rr][ty + 8 * j] * pow_unit(u, pl);
+                acc[j] += (t > 0.f) ? term : -term;
+            }
+        }
+        __syncthreads();
+    }
+    if (i < d.CIg) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            int o = o0 + ty + 8 * j;
+            if (o < d.COg) gw[(size_t)(g * d.COg + o) * d.CIg + i] = acc[j];
+        }
+    }
+}
+
+bool grid_ok(const dim3& g) { return g.y <= 65535u && g.z <= 65535u; }
+
+}  // namespace
+
+int lp_forward(const float* x, const float* w, const Dims& d, float* y, float p, cudaStream_t st) {
+    int rc = inf_forward(x, w, d, y, nullptr, nullptr, 0, st);
+    if (rc != LINF_OK) return rc;
+    dim3 grid((d.R + GT - 1) / GT, (d.COg + GT - 1) / GT, d.G);
+    if (!grid_ok(grid)) return LINF_ERR_DIMS;
+    const PowPlan pl = make_plan(p);
+    const float inv_p = 1.f / p;
+    if (d.HW > 1) lp_forward_generic_kernel<true><<<grid, 256, 0, st>>>(x, w, d, y, pl, inv_p);
+    else lp_forward_generic_kernel<false><<<grid, 256, 0, st>>>(x, w, d, y, pl, inv_p);
+    return launch_status();
+}
+
+int lp_backward_input(const float* g, const float* x, const float* w, const float* y,
+                      const Dims& d, float* gx, float p, cudaStream_t st) {
+    dim3 grid((d.R + GT - 1) / GT, (d.CIg + GT - 1) / GT, d.G);
+    if (!grid_ok(grid)) return LINF_ERR_DIMS;
+    const PowPlan pl = make_plan(p - 1.f);
+    if (d.HW > 1) lp_backward_input_generic_kernel<true><<<grid, 256, 0, st>>>(g, x, w, y, d, gx, pl);
+    else lp_backward_input_generic_kernel<false><<<grid, 256, 0, st>>>(g, x, w, y, d, gx, pl);
+    return launch_status();
+}
+
+int lp_backward_weight(const float* g, const float* x, const float* w, const float* y,
+                       const Dims& d, float* gw, float p, cudaStream_t st) {
+    dim3 grid((d.COg + GT - 1) / GT, (d.CIg + GT - 1) / GT, d.G);
+    if (!grid_ok(grid)) return LINF_ERR_DIMS;
+    const PowPlan pl = make_plan(p - 1.f);
+    if (d.HW > 1) lp_backward_weight_generic_kernel<true><<<grid, 256, 0, st>>>(g, x, w, y, d, gw, pl);
+    else lp_backward_weight_generic_kernel<false><<<grid, 256, 0, st>>>(g, x, w, y, d, gw, pl);
+    return launch_status();
+}
+
+}  // namespace linf

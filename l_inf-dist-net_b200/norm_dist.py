@@ -1,0 +1,296 @@
+"""Host side of the distance neuron: the reference's Python surface on top of liblinfdist.so.
+
+Mirrors model/norm_dist.py of zbh2047/L_inf-dist-net name for name:
+    DistF (:7-47), norm_dist (:49-58), inf_dist_bound (:60-76), MeanNorm (:78-100),
+    NormDistConv (:102-169), NormDist (:171-187), set_p_norm / get_p_norm (:189-198).
+Differences a caller can observe:
+  * `use_custom_cuda_func=False` (the reference's pure-PyTorch debugging branch) is refused:
+    the CUDA library is the only implementation here;
+  * p = inf gradients are produced in a fixed summation order by default ("ordered" mode, see
+    set_backward_mode); the reference's atomicAdd order is undefined;
+  * tensors are validated (CUDA, contiguous, float32) before the call, as the reference's
+    binding does with TORCH_CHECK (model/norm_dist.cpp:3-5).
+"""
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import _lib
+
+_backward_mode = "ordered"
+_workspaces = {}
+
+
+def set_backward_mode(mode):
+    """'ordered': deterministic scatter (ascending source order, bit-reproducible);
+    'atomic': one fused pass with warp-aggregated fp32 atomics (order across warps undefined)."""
+    global _backward_mode
+    if mode not in ("ordered", "atomic"):
+        raise ValueError("backward mode must be 'ordered' or 'atomic'")
+    _backward_mode = mode
+
+
+def get_backward_mode():
+    return _backward_mode
+
+
+def _require(t, name, dtype=torch.float32):
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    if t.dtype != dtype:
+        raise RuntimeError(f"{name} must have dtype {dtype}")
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _workspace(device, nbytes):
+    """Scratch buffer cached per (device, stream); grows, never shrinks."""
+    key = (device.index, _stream())
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def _shape5(x, weight, group):
+    return x.size(0), weight.size(0), x.size(1), group, x.size(2)
+
+
+class DistF(torch.autograd.Function):
+    """y[b,o,hw] = || x[b,g,:,hw] - weight[o,:] ||_p ; x [B,CI,HW], weight [CO,CI/group]."""
+
+    @staticmethod
+    def forward(ctx, x, weight, group, p, tag):
+        lib = _lib.load()
+        _require(x, "input"); _require(weight, "weight")
+        if x.dim() != 3 or weight.dim() != 2:
+            raise RuntimeError("input must be [B, CI, HW] and weight [CO, CI/group]")
+        assert weight.size(1) * group == x.size(1)
+        B, CO, CI, G, HW = _shape5(x, weight, group)
+        y = torch.empty(B, CO, HW, device=x.device, dtype=torch.float32)
+        with torch.cuda.device(x.device):
+            if math.isinf(p):
+                pos = torch.empty(B, CO, HW, device=x.device, dtype=torch.int32)
+                need = lib.linf_inf_dist_forward_workspace_bytes(B, CO, CI, G, HW)
+                if need:
+                    ws = _workspace(x.device, need)
+                    rc = lib.linf_inf_dist_forward_ws(x.data_ptr(), weight.data_ptr(), B, CO, CI, G, HW,
+                                                      y.data_ptr(), pos.data_ptr(), ws.data_ptr(),
+                                                      ws.numel(), _stream())
+                else:
+                    rc = lib.linf_inf_dist_forward(x.data_ptr(), weight.data_ptr(), B, CO, CI, G, HW,
+                                                   y.data_ptr(), pos.data_ptr(), _stream())
+                _lib.check(rc, "inf_dist_forward")
+                ctx.save_for_backward(x, weight, y, pos)
+            elif p > 1:
+                rc = lib.linf_norm_dist_forward(x.data_ptr(), weight.data_ptr(), B, CO, CI, G, HW,
+                                                y.data_ptr(), float(p), _stream())
+                _lib.check(rc, "norm_dist_forward")
+                ctx.save_for_backward(x, weight, y)
+            else:
+                raise NotImplementedError
+        ctx.group, ctx.p, ctx.tag = group, p, tag
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        lib = _lib.load()
+        grad_output = grad_output.contiguous()
+        _require(grad_output, "grad_output")
+        need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        gx = gw = None
+        with torch.cuda.device(grad_output.device):
+            if math.isinf(ctx.p):
+                x, weight, y, pos = ctx.saved_tensors
+                B, CO, CI, G, HW = _shape5(x, weight, ctx.group)
+                if _backward_mode == "atomic":
+                    if need_x:
+                        gx = torch.zeros_like(x)
+                    if need_w:
+                        gw = torch.zeros_like(weight)
+                    if need_x or need_w:
+                        rc = lib.linf_inf_dist_backward_atomic(
+                            grad_output.data_ptr(), pos.data_ptr(), B, CO, CI, G, HW,
+                            gx.data_ptr() if need_x else None, gw.data_ptr() if need_w else None, _stream())
+                        _lib.check(rc, "inf_dist_backward_atomic")
+                else:
+                    if need_x:
+                        gx = torch.empty_like(x)
+                        rc = lib.linf_inf_dist_backward_input(grad_output.data_ptr(), pos.data_ptr(),
+                                                              B, CO, CI, G, HW, gx.data_ptr(), _stream())
+                        _lib.check(rc, "inf_dist_backward_input")
+                    if need_w:
+                        gw = torch.empty_like(weight)
+                        rc = lib.linf_inf_dist_backward_weight(grad_output.data_ptr(), pos.data_ptr(),
+                                                               B, CO, CI, G, HW, gw.data_ptr(), _stream())
+                        _lib.check(rc, "inf_dist_backward_weight")
+            else:
+                x, weight, y = ctx.saved_tensors
+                B, CO, CI, G, HW = _shape5(x, weight, ctx.group)
+                if need_x:
+                    gx = torch.empty_like(x)
+                    rc = lib.linf_norm_dist_backward_input(
+                        grad_output.data_ptr(), x.data_ptr(), weight.data_ptr(), y.data_ptr(),
+                        B, CO, CI, G, HW, gx.data_ptr(), float(ctx.p), _stream())
+                    _lib.check(rc, "norm_dist_backward_input")
+                if need_w:
+                    gw = torch.empty_like(weight)
+                    rc = lib.linf_norm_dist_backward_weight(
+                        grad_output.data_ptr(), x.data_ptr(), weight.data_ptr(), y.data_ptr(),
+                        B, CO, CI, G, HW, gw.data_ptr(), float(ctx.p), _stream())
+                    _lib.check(rc, "norm_dist_backward_weight")
+        return gx, gw, None, None, None
+
+
+def _no_torch_branch():
+    raise RuntimeError("use_custom_cuda_func=False is not available: this package has no "
+                       "PyTorch/CPU implementation of the distance neuron")
+
+
+def norm_dist(input, weight, group, p, use_custom_cuda_func=True, tag=None):
+    if not use_custom_cuda_func:
+        _no_torch_branch()
+    return DistF.apply(input, weight, group, p, tag)
+
+
+def inf_dist_bound(input_lower, input_upper, weight, group, use_custom_cuda_func=True, tag=None):
+    """Interval bounds of an inf-dist layer; returns (output_lower, output_upper), no gradient."""
+    if not use_custom_cuda_func:
+        _no_torch_branch()
+    lib = _lib.load()
+    _require(input_lower, "input_lower"); _require(input_upper, "input_upper"); _require(weight, "weight")
+    B, CO, CI, G, HW = _shape5(input_lower, weight, group)
+    assert weight.size(1) * group == CI and input_upper.shape == input_lower.shape
+    lo = torch.empty(B, CO, HW, device=input_lower.device, dtype=torch.float32)
+    up = torch.empty_like(lo)
+    with torch.cuda.device(input_lower.device):
+        rc = lib.linf_inf_dist_bound_forward(input_lower.data_ptr(), input_upper.data_ptr(), weight.data_ptr(),
+                                             B, CO, CI, G, HW, lo.data_ptr(), up.data_ptr(), _stream())
+    _lib.check(rc, "inf_dist_bound_forward")
+    return lo, up
+
+
+class MeanNorm(nn.Module):
+    """Subtracts the per-channel mean: the batch mean while training (tracking an exponential
+    running mean), the running mean in eval mode."""
+
+    def __init__(self, out_channels, momentum=0.1):
+        super().__init__()
+        self.out_channels = out_channels
+        self.momentum = momentum
+        self.register_buffer("running_mean", torch.zeros(out_channels))
+
+    def forward(self, x):
+        flat = x.reshape(x.size(0), x.size(1), -1)
+        if self.training:
+            mean = flat.mean(dim=-1).mean(dim=0) if x.dim() > 2 else x.mean(dim=0)
+            with torch.no_grad():
+                self.running_mean.mul_(1 - self.momentum).add_(mean, alpha=self.momentum)
+        else:
+            mean = self.running_mean
+        return (flat - mean.unsqueeze(-1)).view_as(x)
+
+    def extra_repr(self):
+        return str(self.out_channels)
+
+
+class NormDistConv(nn.Module):
+    """Convolution-shaped distance layer: every output is the L_p distance between an input
+    patch and a weight row.  state_dict keys match the reference: weight [CO, CI/group, k, k],
+    optional bias [CO], optional normalize.running_mean [CO]."""
+
+    tag_counter = 0
+
+    def __init__(self, in_channels, out_channels, kernel_size, stride=1, padding=0, dilation=1, group=1, p=0,
+                 bias=True, mean_normalize=False, identity_init=True):
+        super().__init__()
+        assert in_channels % group == 0 and out_channels % group == 0
+        self.in_channels, self.out_channels = in_channels, out_channels
+        self.kernel_size, self.stride, self.padding, self.dilation = kernel_size, stride, padding, dilation
+        self.group, self.p = group, p
+        per_group = in_channels // group
+        w = torch.randn(out_channels, per_group, kernel_size, kernel_size)
+        if identity_init and in_channels <= out_channels:
+            rows = torch.arange(out_channels)
+            c = kernel_size // 2
+            w[rows, rows % per_group, c, c] = -10.0
+        self.weight = nn.Parameter(w)
+        self.normalize = MeanNorm(out_channels) if mean_normalize else None
+        self.bias = nn.Parameter(torch.zeros(out_channels)) if bias else None
+        NormDistConv.tag_counter += 1
+        self.tag = NormDistConv.tag_counter
+
+    def _patches(self, t):
+        if self.kernel_size == 1 and self.stride == 1 and self.padding == 0:
+            return t.reshape(t.size(0), t.size(1), -1)      # a dense layer needs no unfold copy
+        return F.unfold(t, self.kernel_size, self.dilation, self.padding, self.stride)
+
+    def _post(self, t):
+        if self.normalize is not None:
+            t = self.normalize(t)
+        if self.bias is not None:
+            t = t + self.bias.view(1, -1, 1, 1)
+        return t
+
+    def forward(self, x, lower=None, upper=None):
+        h, w = x.size(2), x.size(3)
+        ho = (h + 2 * self.padding - self.dilation * (self.kernel_size - 1) - 1) // self.stride + 1
+        wo = (w + 2 * self.padding - self.dilation * (self.kernel_size - 1) - 1) // self.stride + 1
+        weight = self.weight.view(self.weight.size(0), -1)
+        cols = self._patches(x)
+        y = norm_dist(cols, weight, self.group, p=self.p, tag=self.tag).view(x.size(0), -1, ho, wo)
+        y = self._post(y)
+        if lower is None or upper is None:
+            return y, None, None
+        assert math.isinf(self.p) and not self.training
+        lo, up = inf_dist_bound(self._patches(lower), self._patches(upper), weight, self.group, tag=self.tag)
+        return y, self._post(lo.view_as(y)), self._post(up.view_as(y))
+
+    def extra_repr(self):
+        s = f"{self.in_channels}, {self.out_channels}, kernel_size={self.kernel_size}, stride={self.stride}"
+        if self.padding != 0:
+            s += f", padding={self.padding}"
+        if self.dilation != 1:
+            s += f", dilation={self.dilation}"
+        if self.group != 1:
+            s += f", group={self.group}"
+        if self.bias is None:
+            s += ", bias=False"
+        return s
+
+
+class NormDist(NormDistConv):
+    """Dense distance layer: a NormDistConv with a 1 x 1 kernel on [B, C] activations."""
+
+    def __init__(self, in_features, out_features, p=0, bias=True, mean_normalize=False, identity_init=True):
+        super().__init__(in_features, out_features, 1, p=p, bias=bias, mean_normalize=mean_normalize,
+                         identity_init=identity_init)
+
+    def forward(self, x, lower=None, upper=None):
+        as4d = lambda t: None if t is None else t.reshape(t.size(0), t.size(1), 1, 1)
+        y, lo, up = super().forward(as4d(x), as4d(lower), as4d(upper))
+        flat = lambda t: None if t is None else t.reshape(t.size(0), t.size(1))
+        return flat(y), flat(lo), flat(up)
+
+    def extra_repr(self):
+        return f"in_features={self.in_channels}, out_features={self.out_channels}, bias={self.bias is not None}"
+
+
+def set_p_norm(model, p):
+    for m in model.modules():
+        if isinstance(m, NormDistConv):
+            m.p = p
+
+
+def get_p_norm(model):
+    for m in model.modules():
+        if isinstance(m, NormDistConv):
+            return m.p
+    return None

@@ -1,0 +1,256 @@
+"""GPU parity: the CUDA library, called through its C ABI, against the CPU oracle on the same
+seeded inputs, against the golden fixtures of the reference's PyTorch branch, and (when the
+prebuilt library is present) against the reference's own CUDA kernels."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from conftest import ROOT
+from helpers import (GOLDEN, assert_bits_equal, assert_lp_close, c_inf_backward, c_inf_bound,
+                     c_inf_forward, c_lp_backward, c_lp_forward, dev, make_inputs)
+
+pytestmark = pytest.mark.gpu
+
+# (B, CI, CO, HW, G): tiny and ragged shapes (generic path), dense aligned shapes (tiled path,
+# with and without k-splitting), grouped and conv-shaped ones.
+SHAPES = [
+    (1, 1, 1, 1, 1), (1, 15, 1, 1, 1), (1, 16, 10, 1, 1), (1, 17, 17, 1, 1), (7, 17, 10, 1, 1),
+    (3, 18, 12, 5, 3), (2, 8, 6, 4, 2), (5, 784, 10, 1, 1), (6, 32, 48, 1, 4),
+    (33, 100, 65, 1, 1), (64, 128, 128, 1, 1), (130, 784, 200, 1, 1), (16, 64, 256, 1, 4),
+    (70, 36, 300, 1, 1), (9, 3072, 129, 1, 1), (4, 27, 32, 9, 1), (200, 20, 1000, 1, 1),
+]
+
+
+def _ids(s):
+    return "B{}_CI{}_CO{}_HW{}_G{}".format(*s)
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=_ids)
+@pytest.mark.parametrize("use_ws", [True, False], ids=["ws", "nows"])
+def test_inf_forward_bit_exact(cuda, lib, shape, use_ws):
+    B, CI, CO, HW, G = shape
+    x, w, _ = make_inputs(B, CI, CO, HW, G, seed=100 + B + CI)
+    y_ref, pos_ref = oracle.inf_dist_forward(x, w, G)
+    y, pos = c_inf_forward(dev(x), dev(w), G, use_ws=use_ws)
+    assert_bits_equal(y, y_ref, "values")
+    assert_bits_equal(pos, pos_ref, "arg-max")
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=_ids)
+def test_inf_forward_quantised_inputs_many_ties(cuda, lib, shape):
+    """Inputs on a coarse grid produce many exactly tied maxima: the lowest index must win."""
+    B, CI, CO, HW, G = shape
+    rng = np.random.default_rng(7)
+    x = rng.integers(0, 4, (B, CI, HW)).astype(np.float32)
+    w = rng.integers(0, 4, (CO, CI // G)).astype(np.float32)
+    y_ref, pos_ref = oracle.inf_dist_forward(x, w, G)
+    y, pos = c_inf_forward(dev(x), dev(w), G)
+    assert_bits_equal(y, y_ref, "values")
+    assert_bits_equal(pos, pos_ref, "arg-max")
+
+
+def test_inf_forward_special_values(cuda, lib):
+    B, CI, CO = 70, 64, 130
+    x, w, _ = make_inputs(B, CI, CO, 1, 1, seed=5)
+    x[0, :, 0] = w[0]                  # all-zero differences against output 0
+    x[1, 3, 0] = np.nan                # NaN terms are skipped
+    x[2, 5, 0] = np.inf
+    w[7, 9] = -np.inf
+    x[3, :, 0] = 1e-42                 # subnormals survive (no flush to zero)
+    w[11] = 3e-42
+    y_ref, pos_ref = oracle.inf_dist_forward(x, w, 1)
+    y, pos = c_inf_forward(dev(x), dev(w), 1)
+    assert_bits_equal(y, y_ref, "values")
+    assert_bits_equal(pos, pos_ref, "arg-max")
+    assert y_ref[0, 0, 0] == 0 and pos_ref[0, 0, 0] == 0
+    assert 0 < y_ref[3, 11, 0] < 1e-38
+
+
+def test_inf_forward_config1_full_size(cuda, lib):
+    """B=512, Din=784, Dout=5120 (x ~ U[0,1), w ~ N(0,1)): values and arg-max bit-exact."""
+    x, w, g = make_inputs(512, 784, 5120, 1, 1, seed=2020)
+    y_ref, pos_ref = oracle.inf_dist_forward(x, w, 1)
+    for use_ws in (True, False):
+        y, pos = c_inf_forward(dev(x), dev(w), 1, use_ws=use_ws)
+        assert_bits_equal(y, y_ref, "values")
+        assert_bits_equal(pos, pos_ref, "arg-max")
+    gx_ref, gw_ref = oracle.inf_dist_backward(g, pos_ref, 784, 1)
+    gx, gw = c_inf_backward(dev(g), dev(pos_ref), 784, 1, "ordered")
+    assert_bits_equal(gx, gx_ref, "grad_input"); assert_bits_equal(gw, gw_ref, "grad_weight")
+    gx2, gw2 = c_inf_backward(dev(g), dev(pos_ref), 784, 1, "ordered")
+    assert_bits_equal(gx2, gx, "grad_input run-to-run"); assert_bits_equal(gw2, gw, "grad_weight run-to-run")
+    gxa, gwa = c_inf_backward(dev(g), dev(pos_ref), 784, 1, "atomic")
+    np.testing.assert_allclose(gxa.cpu().numpy(), gx_ref, rtol=1e-4, atol=1e-4)
+    np.testing.assert_allclose(gwa.cpu().numpy(), gw_ref, rtol=1e-4, atol=2e-4)
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=_ids)
+def test_inf_backward(cuda, lib, shape):
+    B, CI, CO, HW, G = shape
+    x, w, g = make_inputs(B, CI, CO, HW, G, seed=300 + B + CO)
+    _, pos = oracle.inf_dist_forward(x, w, G)
+    gx_ref, gw_ref = oracle.inf_dist_backward(g, pos, CI, G)
+    gx, gw = c_inf_backward(dev(g), dev(pos), CI, G, "ordered")
+    assert_bits_equal(gx, gx_ref, "ordered grad_input"); assert_bits_equal(gw, gw_ref, "ordered grad_weight")
+    gxa, gwa = c_inf_backward(dev(g), dev(pos), CI, G, "atomic")
+    np.testing.assert_allclose(gxa.cpu().numpy(), gx_ref, rtol=1e-4, atol=1e-4)
+    np.testing.assert_allclose(gwa.cpu().numpy(), gw_ref, rtol=1e-4, atol=1e-4)
+
+
+def test_inf_backward_atomic_exact_when_sums_are_exact(cuda, lib):
+    """With small-integer gradients every partial sum is exact, so any order gives the same bits."""
+    B, CI, CO = 64, 40, 96
+    x, w, _ = make_inputs(B, CI, CO, 1, 1, seed=11)
+    g = np.random.default_rng(3).integers(-8, 9, (B, CO, 1)).astype(np.float32)
+    _, pos = oracle.inf_dist_forward(x, w, 1)
+    gx_ref, gw_ref = oracle.inf_dist_backward(g, pos, CI, 1)
+    gxa, gwa = c_inf_backward(dev(g), dev(pos), CI, 1, "atomic")
+    assert np.array_equal(gxa.cpu().numpy(), gx_ref) and np.array_equal(gwa.cpu().numpy(), gw_ref)
+
+
+BOUND_SHAPES = SHAPES + [(512, 3072, 256, 1, 1), (64, 3072, 512, 1, 4)]
+
+
+@pytest.mark.parametrize("shape", BOUND_SHAPES, ids=_ids)
+def test_inf_bound_bit_exact(cuda, lib, shape):
+    B, CI, CO, HW, G = shape
+    x, w, _ = make_inputs(B, CI, CO, HW, G, seed=500 + CI)
+    eps = np.float32(8.0 / 255.0)
+    lo = np.clip(x - eps, 0, 1).astype(np.float32); up = np.clip(x + eps, 0, 1).astype(np.float32)
+    yl_ref, yu_ref = oracle.inf_dist_bound(lo, up, w, G)
+    yl, yu = c_inf_bound(dev(lo), dev(up), dev(w), G)
+    assert_bits_equal(yl, yl_ref, "lower"); assert_bits_equal(yu, yu_ref, "upper")
+    assert (yl_ref <= yu_ref).all()
+
+
+@pytest.mark.parametrize("kind", ["swapped", "nan", "inf", "degenerate"])
+def test_inf_bound_irregular_inputs(cuda, lib, kind):
+    """lower > upper, NaN and infinities leave the fast rule's domain: the result must still be
+    the literal rule's, bit for bit."""
+    B, CI, CO = 130, 64, 200
+    x, w, _ = make_inputs(B, CI, CO, 1, 1, seed=77)
+    lo = (x - 0.05).astype(np.float32); up = (x + 0.05).astype(np.float32)
+    if kind == "swapped":
+        lo[5, 7, 0], up[5, 7, 0] = up[5, 7, 0], lo[5, 7, 0]
+        lo[100, :, 0], up[100, :, 0] = up[100, :, 0].copy(), lo[100, :, 0].copy()
+    elif kind == "nan":
+        lo[3, 2, 0] = np.nan; up[70, 9, 0] = np.nan; w[4, 4] = np.nan
+    elif kind == "inf":
+        up[1, 1, 0] = np.inf; lo[66, 3, 0] = -np.inf; w[9, 0] = np.inf; w[10, 1] = -np.inf
+    else:
+        up[:] = lo                      # zero-width intervals
+        w[0] = lo[0, :, 0]              # and a weight row equal to an input row
+    yl_ref, yu_ref = oracle.inf_dist_bound(lo, up, w, 1)
+    yl, yu = c_inf_bound(dev(lo), dev(up), dev(w), 1)
+    assert_bits_equal(yl, yl_ref, "lower"); assert_bits_equal(yu, yu_ref, "upper")
+
+
+LP_SHAPES = [(1, 1, 1, 1, 1), (7, 17, 10, 1, 1), (3, 18, 12, 5, 3), (6, 32, 48, 1, 4),
+             (33, 100, 65, 1, 1), (64, 128, 128, 1, 1), (40, 784, 96, 1, 1)]
+
+
+@pytest.mark.parametrize("shape", LP_SHAPES, ids=_ids)
+@pytest.mark.parametrize("p", [8.0, 16.0, 64.0, 11.3, 1.5, 333.25])
+def test_lp_against_oracle(cuda, lib, shape, p):
+    B, CI, CO, HW, G = shape
+    x, w, g = make_inputs(B, CI, CO, HW, G, seed=900 + CI, x_dist="normal")
+    y_ref = oracle.norm_dist_forward(x, w, G, p)
+    y = c_lp_forward(dev(x), dev(w), G, p)
+    assert_lp_close(y, y_ref, "forward", floor=0.0)
+    # gradients from the SAME fp32 output, so only the backward arithmetic is compared
+    gx_ref, gw_ref = oracle.norm_dist_backward(g, x, w, y_ref, G, p)
+    gx, gw = c_lp_backward(dev(g), dev(x), dev(w), dev(y_ref), G, p)
+    # beyond p = 64 the rounding of |t|/y alone, amplified by p - 1, exceeds 1e-5
+    rtol = 1e-5 if p <= 64 else 1e-5 * p / 64
+    assert_lp_close(gx, gx_ref, "grad_input", rtol=rtol)
+    assert_lp_close(gw, gw_ref, "grad_weight", rtol=rtol)
+
+
+def test_lp_against_golden(cuda, lib):
+    z = np.load(os.path.join(GOLDEN, "lp.npz"))
+    cases = sorted({k.split("_")[0] for k in z.files if k.startswith("c")})
+    for c in cases:
+        G = int(z[c + "_shape"][4])
+        x, w, g = z[c + "_x"], z[c + "_w"], z[c + "_g"]
+        for p in (8.0, 16.0, 64.0):
+            tag = f"{c}_p{p:g}"
+            y = c_lp_forward(dev(x), dev(w), G, p)
+            assert_lp_close(y, z[tag + "_y"], f"forward {tag}", floor=0.0)
+            gx, gw = c_lp_backward(dev(g), dev(x), dev(w), y, G, p)
+            assert_lp_close(gx, z[tag + "_gx"], f"grad_input {tag}")
+            assert_lp_close(gw, z[tag + "_gw"], f"grad_weight {tag}")
+
+
+def test_golden_inf_and_bound(cuda, lib):
+    z = np.load(os.path.join(GOLDEN, "inf_forward.npz"))
+    for c in sorted({k.split("_")[0] for k in z.files}):
+        G = int(z[c + "_shape"][4])
+        y, _ = c_inf_forward(dev(z[c + "_x"]), dev(z[c + "_w"]), G)
+        assert_bits_equal(y, z[c + "_y"], f"inf forward {c}")
+    z = np.load(os.path.join(GOLDEN, "inf_bound.npz"))
+    for c in sorted({k.split("_")[0] for k in z.files}):
+        G = int(z[c + "_shape"][4])
+        yl, yu = c_inf_bound(dev(z[c + "_lo"]), dev(z[c + "_up"]), dev(z[c + "_w"]), G)
+        assert_bits_equal(yl, z[c + "_yl"], f"bound lower {c}"); assert_bits_equal(yu, z[c + "_yu"], f"bound upper {c}")
+
+
+def test_lp_config2_slice_and_annealing_points(cuda, lib):
+    """Din = Dout = 5120 as in config 2, on a batch slice the CPU oracle finishes in seconds."""
+    B, CI, CO = 16, 5120, 5120
+    x, w, g = make_inputs(B, CI, CO, 1, 1, seed=2021, x_dist="normal")
+    for p in (8.0, 16.0, 64.0):
+        y_ref = oracle.norm_dist_forward(x, w, 1, p)
+        y = c_lp_forward(dev(x), dev(w), 1, p)
+        assert_lp_close(y, y_ref, f"forward p={p}", floor=0.0)
+        gx_ref, gw_ref = oracle.norm_dist_backward(g, x, w, y_ref, 1, p)
+        gx, gw = c_lp_backward(dev(g), dev(x), dev(w), dev(y_ref), 1, p)
+        assert_lp_close(gx, gx_ref, f"grad_input p={p}"); assert_lp_close(gw, gw_ref, f"grad_weight p={p}")
+
+
+# ---- the reference's own CUDA kernels, when their prebuilt library travelled along ----------
+REF_LIB = os.path.join(ROOT, "oracle", "_ref", "libref_norm_dist.so")
+
+
+@pytest.mark.skipif(not os.path.exists(REF_LIB), reason="reference kernels were not prebuilt")
+@pytest.mark.parametrize("shape", [(33, 100, 65, 1, 1), (130, 784, 200, 1, 1), (16, 64, 256, 1, 4),
+                                   (3, 18, 12, 5, 3), (512, 784, 5120, 1, 1)], ids=_ids)
+def test_against_reference_kernels(cuda, lib, shape):
+    ref = ctypes.CDLL(REF_LIB)
+    B, CI, CO, HW, G = shape
+    x, w, g = make_inputs(B, CI, CO, HW, G, seed=40 + CO)
+    xd, wd, gd = dev(x), dev(w), dev(g)
+    P = lambda t: ctypes.c_void_p(t.data_ptr())
+    torch.cuda.synchronize()
+    # forward + arg-max
+    y_r = torch.empty(B, CO, HW, device="cuda"); pos_r = torch.empty(B, CO, HW, device="cuda", dtype=torch.int32)
+    ref.ref_inf_dist_forward(P(xd), P(wd), B, CO, CI, G, HW, P(y_r), P(pos_r))
+    torch.cuda.synchronize()
+    y, pos = c_inf_forward(xd, wd, G)
+    assert_bits_equal(y, y_r, "values vs reference kernel"); assert_bits_equal(pos, pos_r, "arg-max vs reference kernel")
+    # bounds
+    lo = (xd - 0.03).clamp(0, 1); up = (xd + 0.03).clamp(0, 1)
+    yl_r = torch.empty_like(y_r); yu_r = torch.empty_like(y_r)
+    ref.ref_inf_dist_bound_forward(P(lo), P(up), P(wd), B, CO, CI, G, HW, P(yl_r), P(yu_r))
+    torch.cuda.synchronize()
+    yl, yu = c_inf_bound(lo, up, wd, G)
+    assert_bits_equal(yl, yl_r, "lower vs reference kernel"); assert_bits_equal(yu, yu_r, "upper vs reference kernel")
+    # backward: the reference's atomics are unordered; equal up to summation order
+    gx_r = torch.zeros(B, CI, HW, device="cuda"); gw_r = torch.zeros(CO, CI // G, device="cuda")
+    ref.ref_inf_dist_backward_input(P(gd), P(pos_r), B, CO, CI, G, HW, P(gx_r))
+    ref.ref_inf_dist_backward_weight(P(gd), P(pos_r), B, CO, CI, G, HW, P(gw_r))
+    torch.cuda.synchronize()
+    gx, gw = c_inf_backward(gd, pos, CI, G, "ordered")
+    torch.testing.assert_close(gx, gx_r, rtol=1e-4, atol=2e-4); torch.testing.assert_close(gw, gw_r, rtol=1e-4, atol=2e-4)
+    # finite p: both sides approximate; the reference uses lg2/ex2 approximations
+    if B * CI * CO <= 10 ** 8:
+        xn = dev(make_inputs(B, CI, CO, HW, G, seed=41, x_dist="normal")[0])
+        for p in (8.0, 16.0):
+            yp_r = torch.empty_like(y_r)
+            ref.ref_norm_dist_forward(P(xn), P(wd), B, CO, CI, G, HW, P(yp_r), ctypes.c_float(p))
+            torch.cuda.synchronize()
+            yp = c_lp_forward(xn, wd, G, p)
+            torch.testing.assert_close(yp, yp_r, rtol=2e-5, atol=0)
