@@ -21,8 +21,7 @@ int sm_count() {
     return cached[dev];
 }
 
-extern int inf_forward_mode;
-extern int inf_forward_bk;
+extern int inf_forward_variant;
 
 }  // namespace linf
 
@@ -51,12 +50,11 @@ const char* linf_error_string(int code) {
     }
 }
 
-// Process-wide tuning knobs for benchmarking kernel variants ("inf_forward_mode": 0 scalar
-// sub + 2-input max, 1 scalar sub + 3-input max, 2 packed sub + 3-input max; "inf_forward_bk":
-// 16 or 32).  Not part of the drop-in surface; not thread safe.
+// Process-wide benchmarking knob: key 0 selects the tiled inf-dist forward variant (tile
+// geometry / instruction mix, see the table in inf_forward.cu).  Not part of the drop-in
+// surface; not thread safe.
 int linf_tune_set(int key, int value) {
-    if (key == 0 && value >= 0 && value <= 2) { inf_forward_mode = value; return LINF_OK; }
-    if (key == 1 && (value == 16 || value == 32)) { inf_forward_bk = value; return LINF_OK; }
+    if (key == 0 && value >= 0 && value < 16) { inf_forward_variant = value; return LINF_OK; }
     return LINF_ERR_DIMS;
 }
 

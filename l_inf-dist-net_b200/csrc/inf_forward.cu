@@ -81,12 +81,15 @@ inf_forward_generic_kernel(const float* __restrict__ x, const float* __restrict_
 // =====================================================================================
 // tiled path
 // =====================================================================================
-constexpr int BM = 64, BN = 128, NT = 128;   // CTA tile and thread count
-constexpr int TILE_OUT = BM * BN;            // outputs per tile (64 per thread)
-
-template <int BK>
-struct TileCfg {
-    static constexpr int LD = BK + 4;                 // padded row length in floats
+// Geometry of one kernel variant.  A thread owns 8 rows x TN columns; a warp (4 x 8 lanes)
+// owns 32 rows x 8*TN columns; a CTA has 2 warps along m and NT/64 along n.
+template <int NT_, int TN_, int BK_, int MINB_>
+struct Geo {
+    static constexpr int NT = NT_, TN = TN_, BK = BK_, MINB = MINB_;
+    static constexpr int BM = 64, BN = (NT / 64) * 8 * TN;
+    static constexpr int NOUT = 8 * TN;                 // outputs per thread
+    static constexpr int TILE_OUT = BM * BN;
+    static constexpr int LD = BK + 4;                   // padded row length in floats
     static constexpr int STAGES = (BK == 16) ? 4 : 3;
     static constexpr int STAGE_FLOATS = (BM + BN) * LD;
     static constexpr int SMEM_BYTES = STAGES * STAGE_FLOATS * 4;
@@ -100,9 +103,10 @@ struct TiledParams {
     int tiles_m, tiles_n;  // per group
     int KT;                // k-tiles per output tile
     int n_cta;             // CTAs of the launch (units are dealt evenly to them)
+    int slots_cta;         // CTAs the partial-result area was sized for
     int* tickets;          // one counter per output tile (split mode), else nullptr
-    float* part_val;       // [n_cta][2][TILE_OUT]
-    int* part_cid;         // [n_cta][2][TILE_OUT]
+    float* part_val;       // [slots_cta][2][TILE_OUT]
+    int* part_cid;         // [slots_cta][2][TILE_OUT]
 };
 
 __device__ __forceinline__ long long unit_begin(const TiledParams& p, int c) {
@@ -110,52 +114,51 @@ __device__ __forceinline__ long long unit_begin(const TiledParams& p, int c) {
     return total * c / p.n_cta;
 }
 
-template <int BK>
+template <class GEO>
 __device__ __forceinline__ void load_stage(float* stage, const TiledParams& p, int g, int m0, int n0,
                                            int kt, int tid) {
-    using C = TileCfg<BK>;
-    constexpr int CH = BK / 4;  // 16-byte chunks per row
-    const int k0 = kt * BK;
+    constexpr int CH = GEO::BK / 4;  // 16-byte chunks per row
+    const int k0 = kt * GEO::BK;
     float* As = stage;
-    float* Bs = stage + BM * C::LD;
+    float* Bs = stage + GEO::BM * GEO::LD;
 #pragma unroll
-    for (int q = tid; q < BM * CH; q += NT) {
+    for (int q = tid; q < GEO::BM * CH; q += GEO::NT) {
         int row = q / CH, ch = q % CH;
         int m = min(m0 + row, p.M - 1);
         int k = k0 + ch * 4;
         bool in = k < p.K;
         const float* src = p.x + (size_t)m * p.lda + (size_t)g * p.K + (in ? k : 0);
-        cp_async16(As + row * C::LD + ch * 4, src, in ? 16 : 0);
+        cp_async16(As + row * GEO::LD + ch * 4, src, in ? 16 : 0);
     }
 #pragma unroll
-    for (int q = tid; q < BN * CH; q += NT) {
+    for (int q = tid; q < GEO::BN * CH; q += GEO::NT) {
         int row = q / CH, ch = q % CH;
         int n = min(n0 + row, p.N - 1);
         int k = k0 + ch * 4;
         bool in = k < p.K;
         const float* src = p.w + ((size_t)g * p.N + n) * p.K + (in ? k : 0);
-        cp_async16(Bs + row * C::LD + ch * 4, src, in ? 16 : 0);
+        cp_async16(Bs + row * GEO::LD + ch * 4, src, in ? 16 : 0);
     }
 }
 
-// One k-tile of the (max, |a-b|) product for the 8 x 8 sub-tile of this thread.
+// One k-tile of the (max, |a-b|) product for the 8 x TN sub-tile of this thread.
 // `in` holds the running maxima before the tile, `out` after it (they may alias).
-template <int BK, int MODE>
+template <class GEO, int MODE>
 __device__ __forceinline__ void tile_step(const float* __restrict__ As, const float* __restrict__ Bs,
-                                          const float (&in)[64], float (&out)[64]) {
-    constexpr int LD = TileCfg<BK>::LD;
+                                          const float (&in)[GEO::NOUT], float (&out)[GEO::NOUT]) {
+    constexpr int LD = GEO::LD, TN = GEO::TN;
 #pragma unroll
-    for (int k4 = 0; k4 < BK / 4; ++k4) {
-        ulonglong2 bf[8];
+    for (int k4 = 0; k4 < GEO::BK / 4; ++k4) {
+        ulonglong2 bf[TN];
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+        for (int j = 0; j < TN; ++j)
             bf[j] = *reinterpret_cast<const ulonglong2*>(Bs + (8 * j) * LD + k4 * 4);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const ulonglong2 af = *reinterpret_cast<const ulonglong2*>(As + (4 * i) * LD + k4 * 4);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                float a = (k4 == 0) ? in[i * 8 + j] : out[i * 8 + j];
+            for (int j = 0; j < TN; ++j) {
+                float a = (k4 == 0) ? in[i * TN + j] : out[i * TN + j];
                 float t0, t1, t2, t3;
                 if (MODE == 2) {
                     unpack_f32x2(sub_f32x2(af.x, bf[j].x), t0, t1);
@@ -173,7 +176,7 @@ __device__ __forceinline__ void tile_step(const float* __restrict__ As, const fl
                     a = fmaxf(a, fabsf(t0)); a = fmaxf(a, fabsf(t1));
                     a = fmaxf(a, fabsf(t2)); a = fmaxf(a, fabsf(t3));
                 }
-                out[i * 8 + j] = a;
+                out[i * TN + j] = a;
             }
         }
     }
@@ -181,21 +184,24 @@ __device__ __forceinline__ void tile_step(const float* __restrict__ As, const fl
 
 // After a k-tile: every output whose maximum rose remembers the tile number.  Two 16-bit
 // tile numbers share a register; `ktdup` holds the tile number in both halves.
-__device__ __forceinline__ void note_raises(const float (&before)[64], const float (&after)[64],
-                                            unsigned (&cid)[32], unsigned ktdup) {
+template <int NOUT>
+__device__ __forceinline__ void note_raises(const float (&before)[NOUT], const float (&after)[NOUT],
+                                            unsigned (&cid)[NOUT / 2], unsigned ktdup) {
 #pragma unroll
-    for (int e = 0; e < 64; e += 2) {
+    for (int e = 0; e < NOUT; e += 2) {
         if (after[e] > before[e]) cid[e >> 1] = __byte_perm(cid[e >> 1], ktdup, 0x3254);
         if (after[e + 1] > before[e + 1]) cid[e >> 1] = __byte_perm(cid[e >> 1], ktdup, 0x7610);
     }
 }
 
-__device__ __forceinline__ void cid_set(unsigned (&cid)[32], int e, unsigned v) {
+template <int H>
+__device__ __forceinline__ void cid_set(unsigned (&cid)[H], int e, unsigned v) {
     v &= 0xffffu;
     cid[e >> 1] = (e & 1) ? ((cid[e >> 1] & 0x0000ffffu) | (v << 16)) : ((cid[e >> 1] & 0xffff0000u) | v);
 }
 
-__device__ __forceinline__ int cid_get(const unsigned (&cid)[32], int e) {
+template <int H>
+__device__ __forceinline__ int cid_get(const unsigned (&cid)[H], int e) {
     return (e & 1) ? (int)(cid[e >> 1] >> 16) : (int)(cid[e >> 1] & 0xffffu);
 }
 
@@ -222,17 +228,19 @@ __device__ __forceinline__ int resolve_pos(const float* __restrict__ xrow, const
     return (kbase + best) | (tb < 0.f ? (int)0x80000000 : 0);
 }
 
-template <int BK, int MODE, bool TRACK>
-__global__ void __launch_bounds__(NT, 2)
+template <class GEO, int MODE, bool TRACK>
+__global__ void __launch_bounds__(GEO::NT, GEO::MINB)
 inf_forward_tiled_kernel(const TiledParams p) {
-    using C = TileCfg<BK>;
+    constexpr int NT = GEO::NT, TN = GEO::TN, NOUT = GEO::NOUT, BK = GEO::BK, TILE_OUT = GEO::TILE_OUT;
+    constexpr int BM = GEO::BM, BN = GEO::BN, STAGES = GEO::STAGES, STAGE_FLOATS = GEO::STAGE_FLOATS;
+    constexpr int NB = TRACK ? NOUT : 2;        // size of the second accumulator set / tile-number set
     extern __shared__ __align__(16) float smem[];
     __shared__ int s_last;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int wm = warp & 1, wn = warp >> 1, lm = lane >> 3, ln = lane & 7;
-    const int row_off = wm * 32 + lm;   // + 4*i
-    const int col_off = wn * 64 + ln;   // + 8*j
+    const int row_off = wm * 32 + lm;            // + 4*i
+    const int col_off = wn * (8 * TN) + ln;      // + 8*j
 
     const int tiles_per_group = p.tiles_m * p.tiles_n;
     long long u = unit_begin(p, blockIdx.x);
@@ -247,55 +255,53 @@ inf_forward_tiled_kernel(const TiledParams p) {
         const int tg = tile - g * tiles_per_group;
         const int n0 = (tg / p.tiles_m) * BN, m0 = (tg % p.tiles_m) * BM;
 
-        float accA[64];
-        float accB[TRACK ? 64 : 1];
-        unsigned cid[TRACK ? 32 : 1];
+        float accA[NOUT];
+        float accB[NB];
+        unsigned cid[NB / 2];
 #pragma unroll
-        for (int e = 0; e < 64; ++e) accA[e] = 0.f;
-        if (TRACK) {
+        for (int e = 0; e < NOUT; ++e) accA[e] = 0.f;
 #pragma unroll
-            for (int e = 0; e < 32; ++e) cid[e] = (unsigned)kt0 * 0x10001u;
-        }
+        for (int e = 0; e < NB / 2; ++e) cid[e] = (unsigned)kt0 * 0x10001u;
 
         // ---- software pipeline over the k-tiles of this segment ----
         __syncthreads();   // previous segment is done with the ring
 #pragma unroll
-        for (int s = 0; s < C::STAGES - 1; ++s) {
-            if (kt0 + s < kt1) load_stage<BK>(smem + s * C::STAGE_FLOATS, p, g, m0, n0, kt0 + s, tid);
+        for (int s = 0; s < STAGES - 1; ++s) {
+            if (kt0 + s < kt1) load_stage<GEO>(smem + s * STAGE_FLOATS, p, g, m0, n0, kt0 + s, tid);
             cp_async_commit();
         }
-        int rd = 0, wr = C::STAGES - 1;
+        int rd = 0, wr = STAGES - 1;
         for (int kt = kt0; kt < kt1; kt += 2) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const int ktc = kt + h;
                 if (ktc < kt1) {
-                    cp_async_wait<C::STAGES - 2>();
+                    cp_async_wait<STAGES - 2>();
                     __syncthreads();
-                    if (ktc + C::STAGES - 1 < kt1)
-                        load_stage<BK>(smem + wr * C::STAGE_FLOATS, p, g, m0, n0, ktc + C::STAGES - 1, tid);
+                    if (ktc + STAGES - 1 < kt1)
+                        load_stage<GEO>(smem + wr * STAGE_FLOATS, p, g, m0, n0, ktc + STAGES - 1, tid);
                     cp_async_commit();
-                    const float* As = smem + rd * C::STAGE_FLOATS + row_off * C::LD;
-                    const float* Bs = smem + rd * C::STAGE_FLOATS + (BM + col_off) * C::LD;
-                    if (TRACK) {
+                    const float* As = smem + rd * STAGE_FLOATS + row_off * GEO::LD;
+                    const float* Bs = smem + rd * STAGE_FLOATS + (BM + col_off) * GEO::LD;
+                    if constexpr (TRACK) {
                         if (h == 0) {
-                            tile_step<BK, MODE>(As, Bs, accA, reinterpret_cast<float(&)[64]>(accB));
-                            note_raises(accA, reinterpret_cast<float(&)[64]>(accB),
-                                        reinterpret_cast<unsigned(&)[32]>(cid), (unsigned)ktc * 0x10001u);
+                            tile_step<GEO, MODE>(As, Bs, accA, accB);
+                            note_raises<NOUT>(accA, accB, cid, (unsigned)ktc * 0x10001u);
                         } else {
-                            tile_step<BK, MODE>(As, Bs, reinterpret_cast<float(&)[64]>(accB), accA);
-                            note_raises(reinterpret_cast<float(&)[64]>(accB), accA,
-                                        reinterpret_cast<unsigned(&)[32]>(cid), (unsigned)ktc * 0x10001u);
+                            tile_step<GEO, MODE>(As, Bs, accB, accA);
+                            note_raises<NOUT>(accB, accA, cid, (unsigned)ktc * 0x10001u);
                         }
                     } else {
-                        tile_step<BK, MODE>(As, Bs, accA, accA);
+                        tile_step<GEO, MODE>(As, Bs, accA, accA);
                     }
-                    rd = (rd + 1 == C::STAGES) ? 0 : rd + 1;
-                    wr = (wr + 1 == C::STAGES) ? 0 : wr + 1;
+                    rd = (rd + 1 == STAGES) ? 0 : rd + 1;
+                    wr = (wr + 1 == STAGES) ? 0 : wr + 1;
                 } else if (TRACK && h == 1) {
-                    // odd number of k-tiles: the result sits in accB
+                    // odd number of k-tiles: the result sits in the second set
+                    if constexpr (TRACK) {
 #pragma unroll
-                    for (int e = 0; e < 64; ++e) accA[e] = reinterpret_cast<float(&)[64]>(accB)[e];
+                        for (int e = 0; e < NOUT; ++e) accA[e] = accB[e];
+                    }
                 }
             }
         }
@@ -308,9 +314,9 @@ inf_forward_tiled_kernel(const TiledParams p) {
             // park the partial result, then take a ticket: the last arrival merges
             const size_t slot = ((size_t)blockIdx.x * 2 + (seg ? 1 : 0)) * TILE_OUT;
 #pragma unroll
-            for (int e = 0; e < 64; ++e) {
+            for (int e = 0; e < NOUT; ++e) {
                 p.part_val[slot + e * NT + tid] = accA[e];
-                if (TRACK) p.part_cid[slot + e * NT + tid] = cid_get(reinterpret_cast<unsigned(&)[32]>(cid), e);
+                if constexpr (TRACK) p.part_cid[slot + e * NT + tid] = cid_get(cid, e);
             }
             __threadfence();
             __syncthreads();
@@ -335,24 +341,22 @@ inf_forward_tiled_kernel(const TiledParams p) {
                     const int s2 = ((int)(unit_begin(p, c) / p.KT) == tile) ? 0 : 1;
                     const size_t sl = ((size_t)c * 2 + s2) * TILE_OUT;
 #pragma unroll
-                    for (int e = 0; e < 64; ++e) {
+                    for (int e = 0; e < NOUT; ++e) {
                         const float v = __ldcg(p.part_val + sl + e * NT + tid);
                         if (v >= accA[e]) {
                             accA[e] = v;
-                            if (TRACK) cid_set(reinterpret_cast<unsigned(&)[32]>(cid), e,
-                                               (unsigned)__ldcg(p.part_cid + sl + e * NT + tid));
+                            if constexpr (TRACK) cid_set(cid, e, (unsigned)__ldcg(p.part_cid + sl + e * NT + tid));
                         }
                     }
                 }
                 for (int c = (int)blockIdx.x + 1; c <= c_hi; ++c) {
                     const size_t sl = ((size_t)c * 2 + 0) * TILE_OUT;   // always that CTA's first segment
 #pragma unroll
-                    for (int e = 0; e < 64; ++e) {
+                    for (int e = 0; e < NOUT; ++e) {
                         const float v = __ldcg(p.part_val + sl + e * NT + tid);
                         if (v > accA[e]) {
                             accA[e] = v;
-                            if (TRACK) cid_set(reinterpret_cast<unsigned(&)[32]>(cid), e,
-                                               (unsigned)__ldcg(p.part_cid + sl + e * NT + tid));
+                            if constexpr (TRACK) cid_set(cid, e, (unsigned)__ldcg(p.part_cid + sl + e * NT + tid));
                         }
                     }
                 }
@@ -366,17 +370,15 @@ inf_forward_tiled_kernel(const TiledParams p) {
                 if (m < p.M) {
                     const float* xrow = p.x + (size_t)m * p.lda + (size_t)g * p.K;
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
+                    for (int j = 0; j < TN; ++j) {
                         const int n = n0 + col_off + 8 * j;
                         if (n < p.N) {
-                            const float yv = accA[i * 8 + j];
+                            const float yv = accA[i * TN + j];
                             const size_t o = (size_t)m * p.ldo + (size_t)g * p.N + n;
                             p.y[o] = yv;
-                            if (TRACK) {
+                            if constexpr (TRACK) {
                                 const float* wrow = p.w + ((size_t)g * p.N + n) * p.K;
-                                p.pos[o] = resolve_pos<BK>(
-                                    xrow, wrow, cid_get(reinterpret_cast<unsigned(&)[32]>(cid), i * 8 + j),
-                                    p.K, yv);
+                                p.pos[o] = resolve_pos<BK>(xrow, wrow, cid_get(cid, i * TN + j), p.K, yv);
                             }
                         }
                     }
@@ -388,25 +390,34 @@ inf_forward_tiled_kernel(const TiledParams p) {
     }
 }
 
-template <int BK, int MODE, bool TRACK>
-int launch_tiled(const TiledParams& p, cudaStream_t st) {
-    using C = TileCfg<BK>;
-    auto kern = inf_forward_tiled_kernel<BK, MODE, TRACK>;
-    static bool configured[16] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 16 && !configured[dev]) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
-            return LINF_ERR_LAUNCH;
-        configured[dev] = true;
-    }
-    kern<<<p.n_cta, NT, C::SMEM_BYTES, st>>>(p);
-    return launch_status();
-}
-
 size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
+// ---- variant table ------------------------------------------------------------------------
+struct Variant {
+    int bm, bn, bk, nt, min_blocks, smem;
+    void (*kern_track)(const TiledParams);
+    void (*kern_plain)(const TiledParams);
+};
+
+template <class GEO, int MODE>
+constexpr Variant make_variant() {
+    return Variant{GEO::BM, GEO::BN, GEO::BK, GEO::NT, GEO::MINB, GEO::SMEM_BYTES,
+                   inf_forward_tiled_kernel<GEO, MODE, true>, inf_forward_tiled_kernel<GEO, MODE, false>};
+}
+
+const Variant kVariants[] = {
+    make_variant<Geo<256, 4, 16, 2>, 2>(),   // 0: 8x4 per thread, 256 threads, 2 CTAs/SM
+    make_variant<Geo<128, 8, 16, 2>, 2>(),   // 1: 8x8 per thread, 128 threads, 2 CTAs/SM
+    make_variant<Geo<128, 4, 16, 3>, 2>(),   // 2: 8x4 per thread, 128 threads (64x64 tile), 3 CTAs/SM (default)
+    make_variant<Geo<256, 4, 16, 2>, 0>(),   // 3: as 0 with scalar sub + 2-input max
+    make_variant<Geo<128, 4, 16, 4>, 2>(),   // 4: 8x4 per thread, 128 threads, 4 CTAs/SM
+    make_variant<Geo<256, 4, 32, 2>, 2>(),   // 5: as 0 with 32-wide k-tiles
+};
+constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
+
 }  // namespace
+
+int inf_forward_variant = 2;   // index into kVariants (benchmarking knob)
 
 // Shapes the tiled path accepts.
 static bool tiled_ok(const float* x, const float* w, const Dims& d) {
@@ -414,28 +425,32 @@ static bool tiled_ok(const float* x, const float* w, const Dims& d) {
            d.COg >= 32 && (d.CIg + 15) / 16 < 65536;
 }
 
-static int tiled_tiles(const Dims& d) {
-    return ((d.R + BM - 1) / BM) * ((d.COg + BN - 1) / BN) * d.G;
+static const Variant& cur_variant() {
+    int v = inf_forward_variant;
+    return kVariants[(v >= 0 && v < kNumVariants) ? v : 0];
+}
+
+static int tiled_tiles(const Dims& d, const Variant& v) {
+    return ((d.R + v.bm - 1) / v.bm) * ((d.COg + v.bn - 1) / v.bn) * d.G;
 }
 
 // Splitting k-tiles across CTAs pays when whole tiles would leave a large part of the last
 // wave of CTAs idle.
-static bool want_split(const Dims& d) {
-    const int slots = 2 * sm_count();
-    const int tiles = tiled_tiles(d);
+static bool want_split(const Dims& d, const Variant& v) {
+    const int slots = v.min_blocks * sm_count();
+    const int tiles = tiled_tiles(d, v);
     const int waves = (tiles + slots - 1) / slots;
     return (double)tiles / ((double)waves * slots) < 0.9;
 }
 
 size_t inf_forward_workspace(const Dims& d) {
     if (d.HW != 1 || (d.CIg % 4) != 0 || d.COg < 32) return 0;
-    if (!want_split(d)) return 0;
-    const size_t n_cta = 2 * (size_t)sm_count();
-    return align256((size_t)tiled_tiles(d) * sizeof(int)) + n_cta * 2 * TILE_OUT * (sizeof(float) + sizeof(int));
+    const Variant& v = cur_variant();
+    if (!want_split(d, v)) return 0;
+    const size_t n_cta = (size_t)v.min_blocks * sm_count();
+    return align256((size_t)tiled_tiles(d, v) * sizeof(int)) +
+           n_cta * 2 * v.bm * v.bn * (sizeof(float) + sizeof(int));
 }
-
-int inf_forward_mode = 2;   // instruction variant of the tiled kernel (2 = packed sub + 3-input max)
-int inf_forward_bk = 16;
 
 int inf_forward(const float* x, const float* w, const Dims& d, float* y, int* pos,
                 void* ws, size_t ws_bytes, cudaStream_t st) {
@@ -446,38 +461,36 @@ int inf_forward(const float* x, const float* w, const Dims& d, float* y, int* po
         else inf_forward_generic_kernel<false><<<grid, 256, 0, st>>>(x, w, d, y, pos);
         return launch_status();
     }
+    const Variant& v = cur_variant();
     TiledParams p;
     p.x = x; p.w = w; p.y = y; p.pos = pos;
     p.M = d.R; p.N = d.COg; p.K = d.CIg; p.G = d.G;
     p.lda = d.CI; p.ldo = d.CO;
-    p.tiles_m = (d.R + BM - 1) / BM; p.tiles_n = (d.COg + BN - 1) / BN;
-    const int BK = inf_forward_bk;
-    p.KT = (d.CIg + BK - 1) / BK;
+    p.tiles_m = (d.R + v.bm - 1) / v.bm; p.tiles_n = (d.COg + v.bn - 1) / v.bn;
+    p.KT = (d.CIg + v.bk - 1) / v.bk;
     const int tiles = p.tiles_m * p.tiles_n * d.G;
     p.tickets = nullptr; p.part_val = nullptr; p.part_cid = nullptr;
     p.n_cta = tiles;
+    p.slots_cta = 0;
     const size_t need = inf_forward_workspace(d);
-    if (ws != nullptr && need != 0 && want_split(d)) {
+    if (ws != nullptr && need != 0) {
         if (ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 255u)) return LINF_ERR_WORKSPACE;
         const size_t tick_bytes = align256((size_t)tiles * sizeof(int));
-        long long total = (long long)tiles * p.KT;
-        p.n_cta = (int)min((long long)2 * sm_count(), total);
+        const long long total = (long long)tiles * p.KT;
+        p.slots_cta = v.min_blocks * sm_count();
+        p.n_cta = (int)min((long long)p.slots_cta, total);
         p.tickets = reinterpret_cast<int*>(ws);
         p.part_val = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + tick_bytes);
-        p.part_cid = reinterpret_cast<int*>(p.part_val + (size_t)2 * sm_count() * 2 * TILE_OUT);
+        p.part_cid = reinterpret_cast<int*>(p.part_val + (size_t)p.slots_cta * 2 * v.bm * v.bn);
         if (cudaMemsetAsync(p.tickets, 0, tick_bytes, st) != cudaSuccess) return LINF_ERR_LAUNCH;
     }
-    const int mode = inf_forward_mode;
-    const bool track = pos != nullptr;
-#define LINF_DISPATCH(BKV, MODEV)                                                     \
-    if (BK == BKV && mode == MODEV)                                                   \
-        return track ? launch_tiled<BKV, MODEV, true>(p, st) : launch_tiled<BKV, MODEV, false>(p, st);
-    LINF_DISPATCH(16, 2)
-    LINF_DISPATCH(16, 1)
-    LINF_DISPATCH(16, 0)
-    LINF_DISPATCH(32, 2)
-#undef LINF_DISPATCH
-    return LINF_ERR_LAUNCH;
+    auto kern = pos != nullptr ? v.kern_track : v.kern_plain;
+    // opting in to > 48 KB of dynamic shared memory is per function and per device; it is cheap
+    // enough to repeat on every call and keeps the library free of mutable global state
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, v.smem) != cudaSuccess)
+        return LINF_ERR_LAUNCH;
+    kern<<<p.n_cta, v.nt, v.smem, st>>>(p);
+    return launch_status();
 }
 
 }  // namespace linf
