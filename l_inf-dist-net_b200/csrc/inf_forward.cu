@@ -90,7 +90,7 @@ struct Geo {
     static constexpr int NOUT = 8 * TN;                 // outputs per thread
     static constexpr int TILE_OUT = BM * BN;
     static constexpr int LD = BK + 4;                   // padded row length in floats
-    static constexpr int STAGES = (BK == 16) ? 4 : 3;
+    static constexpr int STAGES = (BK <= 16) ? 4 : 3;
     static constexpr int STAGE_FLOATS = (BM + BN) * LD;
     static constexpr int SMEM_BYTES = STAGES * STAGE_FLOATS * 4;
 };
@@ -153,6 +153,34 @@ __device__ __forceinline__ void tile_step(const float* __restrict__ As, const fl
 #pragma unroll
         for (int j = 0; j < TN; ++j)
             bf[j] = *reinterpret_cast<const ulonglong2*>(Bs + (8 * j) * LD + k4 * 4);
+        if (MODE == 3) {
+            // software-pipelined order: the packed subtractions of row i+1 are written between
+            // the 3-input maxima of row i, so that FMA-pipe and ALU-pipe instructions alternate
+            unsigned long long dc[TN][2], dn[TN][2];
+            {
+                const ulonglong2 af = *reinterpret_cast<const ulonglong2*>(As + k4 * 4);
+#pragma unroll
+                for (int j = 0; j < TN; ++j) { dc[j][0] = sub_f32x2(af.x, bf[j].x); dc[j][1] = sub_f32x2(af.y, bf[j].y); }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                ulonglong2 af = make_ulonglong2(0, 0);
+                if (i < 7) af = *reinterpret_cast<const ulonglong2*>(As + (4 * (i + 1)) * LD + k4 * 4);
+#pragma unroll
+                for (int j = 0; j < TN; ++j) {
+                    if (i < 7) { dn[j][0] = sub_f32x2(af.x, bf[j].x); dn[j][1] = sub_f32x2(af.y, bf[j].y); }
+                    float a = (k4 == 0) ? in[i * TN + j] : out[i * TN + j];
+                    float t0, t1, t2, t3;
+                    unpack_f32x2(dc[j][0], t0, t1); unpack_f32x2(dc[j][1], t2, t3);
+                    a = max3(a, fabsf(t0), fabsf(t1));
+                    a = max3(a, fabsf(t2), fabsf(t3));
+                    out[i * TN + j] = a;
+                }
+#pragma unroll
+                for (int j = 0; j < TN; ++j) { dc[j][0] = dn[j][0]; dc[j][1] = dn[j][1]; }
+            }
+            continue;
+        }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const ulonglong2 af = *reinterpret_cast<const ulonglong2*>(As + (4 * i) * LD + k4 * 4);
@@ -412,6 +440,10 @@ const Variant kVariants[] = {
     make_variant<Geo<256, 4, 16, 2>, 0>(),   // 3: as 0 with scalar sub + 2-input max
     make_variant<Geo<128, 4, 16, 4>, 2>(),   // 4: 8x4 per thread, 128 threads, 4 CTAs/SM
     make_variant<Geo<256, 4, 32, 2>, 2>(),   // 5: as 0 with 32-wide k-tiles
+    make_variant<Geo<128, 4, 16, 3>, 3>(),   // 6: as 2, subtractions and maxima interleaved in source order
+    make_variant<Geo<128, 4, 16, 3>, 1>(),   // 7: as 2 with scalar sub + 3-input max
+    make_variant<Geo<128, 4, 32, 3>, 2>(),   // 8: as 2 with 32-wide k-tiles
+    make_variant<Geo<128, 4, 8, 3>, 2>(),    // 9: as 2 with 8-wide k-tiles
 };
 constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
 
