@@ -84,6 +84,11 @@ int inf_backward_input(const float* g, const int* pos, const Dims& d, float* gx,
 int inf_backward_weight(const float* g, const int* pos, const Dims& d, float* gw, cudaStream_t st);
 int inf_backward_atomic(const float* g, const int* pos, const Dims& d, float* gx, float* gw,
                         cudaStream_t st);
+// few output channels per group (skinny.cu)
+bool skinny_ok(const Dims& d, const void* a, const void* b, const void* c);
+int inf_forward_skinny(const float* x, const float* w, const Dims& d, float* y, int* pos, cudaStream_t st);
+int inf_bound_skinny(const float* xl, const float* xu, const float* w, const Dims& d, float* yl, float* yu,
+                     cudaStream_t st);
 int lp_forward(const float* x, const float* w, const Dims& d, float* y, float p, cudaStream_t st);
 int lp_backward_input(const float* g, const float* x, const float* w, const float* y,
                       const Dims& d, float* gx, float p, cudaStream_t st);

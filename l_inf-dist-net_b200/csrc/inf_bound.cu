@@ -253,6 +253,7 @@ int inf_bound(const float* xl, const float* xu, const float* w, const Dims& d,
     const bool tiled = d.HW == 1 && (d.CIg % 4) == 0 && aligned16(xl) && aligned16(xu) && aligned16(w) &&
                        d.COg >= 32;
     if (!tiled) {
+        if (skinny_ok(d, xl, xu, w)) return inf_bound_skinny(xl, xu, w, d, yl, yu, st);
         dim3 grid((d.R + GT - 1) / GT, (d.COg + GT - 1) / GT, d.G);
         if (grid.y > 65535u || grid.z > 65535u) return LINF_ERR_DIMS;
         if (d.HW > 1) inf_bound_generic_kernel<true><<<grid, 256, 0, st>>>(xl, xu, w, d, yl, yu);

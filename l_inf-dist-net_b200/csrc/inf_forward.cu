@@ -487,6 +487,7 @@ size_t inf_forward_workspace(const Dims& d) {
 int inf_forward(const float* x, const float* w, const Dims& d, float* y, int* pos,
                 void* ws, size_t ws_bytes, cudaStream_t st) {
     if (!tiled_ok(x, w, d)) {
+        if (skinny_ok(d, x, w, nullptr)) return inf_forward_skinny(x, w, d, y, pos, st);
         dim3 grid((d.R + GT - 1) / GT, (d.COg + GT - 1) / GT, d.G);
         if (grid.y > 65535u || grid.z > 65535u) return LINF_ERR_DIMS;
         if (d.HW > 1) inf_forward_generic_kernel<true><<<grid, 256, 0, st>>>(x, w, d, y, pos);

@@ -22,6 +22,8 @@ SHAPES = [
     (3, 18, 12, 5, 3), (2, 8, 6, 4, 2), (5, 784, 10, 1, 1), (6, 32, 48, 1, 4),
     (33, 100, 65, 1, 1), (64, 128, 128, 1, 1), (130, 784, 200, 1, 1), (16, 64, 256, 1, 4),
     (70, 36, 300, 1, 1), (9, 3072, 129, 1, 1), (4, 27, 32, 9, 1), (200, 20, 1000, 1, 1),
+    # few output channels: lanes split the reduction (classifier layer 5120 -> 10 and neighbours)
+    (37, 5120, 10, 1, 1), (5, 256, 3, 1, 1), (11, 512, 31, 1, 1), (6, 1024, 40, 1, 4), (3, 128, 17, 1, 1),
 ]
 
 
