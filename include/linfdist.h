@@ -78,6 +78,30 @@ int linf_inf_dist_forward_ws(const float* input, const float* weight,
                              void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * The same forward for callers that are not allowed to allocate device memory -- for example a
+ * plug-in of a framework that owns all device memory through its own pool, or a deployment whose
+ * memory is sized once at start-up and where a later cudaMalloc counts as a fault.  Such a caller
+ * cannot supply the workspace of linf_inf_dist_forward_ws, so the scratch lives in the library
+ * itself: a fixed device array of LINF_NOALLOC_SCRATCH_BYTES that every GPU which loads the
+ * library keeps resident until the process exits.  The call itself allocates nothing (no
+ * cudaMalloc / cudaFree, no allocating library routine); inputs and outputs are the caller's.
+ *   - Limit: returns LINF_ERR_TOO_LARGE when the layer would need more scratch than the array
+ *     holds (the need grows with the SM count of the GPU and, slowly, with the number of output
+ *     tiles; on a 148-SM B200 every layer the library accepts fits).
+ *   - The first call on each device looks up the device address of the array (with that device
+ *     current).  Make that first call once during set-up, before any stream capture begins.
+ *   - All calls on one GPU share the one array, and it keeps whatever the last call left there;
+ *     the call clears the part that has to start at zero.  Two calls that overlap on the same
+ *     GPU (different streams or threads) race on it: run them one after the other.
+ * Results are identical to linf_inf_dist_forward.  This entry point has no counterpart in the
+ * reference, whose kernels use no scratch memory.
+ */
+#define LINF_NOALLOC_SCRATCH_BYTES (30u * 1024u * 1024u)
+int linf_inf_dist_forward_noalloc(const float* input, const float* weight,
+                                  int B, int CO, int CI, int G, int HW,
+                                  float* output, int* pos, void* stream);
+
+/*
  * Interval propagation through an inf-dist layer in one pass:
  *   tL = lower - w, tU = upper - w
  *   output_upper = max_i max(|tL|, |tU|)

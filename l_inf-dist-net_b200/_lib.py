@@ -6,7 +6,7 @@ import subprocess
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "liblinfdist.so")
 CSRC = os.path.join(_HERE, "csrc")
-SOURCES = ["api.cu", "inf_forward.cu", "inf_bound.cu", "inf_backward.cu", "lp.cu", "skinny.cu"]
+SOURCES = ["api.cu", "inf_forward.cu", "inf_bound.cu", "inf_backward.cu", "lp.cu", "no_alloc.cu", "skinny.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "--shared", "-Xcompiler", "-fPIC"]
 
@@ -21,6 +21,7 @@ _PROTOS = {
     "linf_inf_dist_forward": [_F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F, _F],
     "linf_inf_dist_forward_workspace_bytes": [_INT, _INT, _INT, _INT, _INT],
     "linf_inf_dist_forward_ws": [_F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F, _F, ctypes.c_size_t, _F],
+    "linf_inf_dist_forward_noalloc": [_F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F, _F],
     "linf_inf_dist_bound_forward": [_F, _F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F, _F],
     "linf_inf_dist_backward_input": [_F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F],
     "linf_inf_dist_backward_weight": [_F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F],
