@@ -89,6 +89,11 @@ bool skinny_ok(const Dims& d, const void* a, const void* b, const void* c);
 int inf_forward_skinny(const float* x, const float* w, const Dims& d, float* y, int* pos, cudaStream_t st);
 int inf_bound_skinny(const float* xl, const float* xu, const float* w, const Dims& d, float* yl, float* yu,
                      cudaStream_t st);
+// register-tiled finite-p kernels for dense, aligned layers (lp_tiled.cu)
+bool lp_tiled_ok(const Dims& d, const void* a, const void* b, const void* c, const void* e, const void* f);
+int lp_forward_tiled(const float* x, const float* w, const Dims& d, float* y, float p, cudaStream_t st);
+int lp_backward_tiled(const float* g, const float* x, const float* w, const float* y, const Dims& d,
+                      float* out, float p, bool wrt_weight, cudaStream_t st);
 int lp_forward(const float* x, const float* w, const Dims& d, float* y, float p, cudaStream_t st);
 int lp_backward_input(const float* g, const float* x, const float* w, const float* y,
                       const Dims& d, float* gx, float p, cudaStream_t st);

@@ -216,6 +216,7 @@ bool grid_ok(const dim3& g) { return g.y <= 65535u && g.z <= 65535u; }
 int lp_forward(const float* x, const float* w, const Dims& d, float* y, float p, cudaStream_t st) {
     int rc = inf_forward(x, w, d, y, nullptr, nullptr, 0, st);
     if (rc != LINF_OK) return rc;
+    if (lp_tiled_ok(d, x, w, y, nullptr, nullptr)) return lp_forward_tiled(x, w, d, y, p, st);
     dim3 grid((d.R + GT - 1) / GT, (d.COg + GT - 1) / GT, d.G);
     if (!grid_ok(grid)) return LINF_ERR_DIMS;
     const PowPlan pl = make_plan(p);
@@ -227,6 +228,10 @@ int lp_forward(const float* x, const float* w, const Dims& d, float* y, float p,
 
 int lp_backward_input(const float* g, const float* x, const float* w, const float* y,
                       const Dims& d, float* gx, float p, cudaStream_t st) {
+    if (lp_tiled_ok(d, x, w, y, g, gx)) {
+        const int rc = lp_backward_tiled(g, x, w, y, d, gx, p, false, st);
+        if (rc >= 0) return rc;             // negative: exponent beyond the tiled instantiations
+    }
     dim3 grid((d.R + GT - 1) / GT, (d.CIg + GT - 1) / GT, d.G);
     if (!grid_ok(grid)) return LINF_ERR_DIMS;
     const PowPlan pl = make_plan(p - 1.f);
@@ -237,6 +242,10 @@ int lp_backward_input(const float* g, const float* x, const float* w, const floa
 
 int lp_backward_weight(const float* g, const float* x, const float* w, const float* y,
                        const Dims& d, float* gw, float p, cudaStream_t st) {
+    if (lp_tiled_ok(d, x, w, y, g, gw)) {
+        const int rc = lp_backward_tiled(g, x, w, y, d, gw, p, true, st);
+        if (rc >= 0) return rc;
+    }
     dim3 grid((d.COg + GT - 1) / GT, (d.CIg + GT - 1) / GT, d.G);
     if (!grid_ok(grid)) return LINF_ERR_DIMS;
     const PowPlan pl = make_plan(p - 1.f);
