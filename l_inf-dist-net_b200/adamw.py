@@ -7,6 +7,7 @@ import math
 import torch
 from torch.optim import Optimizer
 
+from . import _lib
 from .norm_dist import get_p_norm
 
 
@@ -18,6 +19,12 @@ class AdamW(Optimizer):
             raise ValueError("betas must lie in [0, 1)")
         groups = [{"params": p, "module": m} for m in model.modules() for p in m.parameters(False)]
         super().__init__(groups, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
+
+    @staticmethod
+    def _fused_ok(p):
+        return (p.is_cuda and p.dtype == torch.float32 and p.is_contiguous() and p.grad.is_contiguous()
+                and p.grad.dtype == torch.float32 and p.dim() >= 1 and p.numel() > 0
+                and p.numel() // p.size(0) <= 51200)
 
     @staticmethod
     def _decay(p, p_norm, lr_wd, eps):
@@ -48,13 +55,24 @@ class AdamW(Optimizer):
                     continue
                 if p.grad.is_sparse:
                     raise RuntimeError("AdamW does not support sparse gradients")
-                self._decay(p, get_p_norm(group["module"]), group["lr"] * group["weight_decay"], group["eps"])
                 state = self.state[p]
                 if not state:
                     state["step"] = 0
                     state["exp_avg"] = torch.zeros_like(p, memory_format=torch.preserve_format)
                     state["exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.preserve_format)
                 state["step"] += 1
+                p_norm = get_p_norm(group["module"])
+                if self._fused_ok(p):
+                    # CUDA tensors: one fused launch per tensor (csrc/adamw.cu)
+                    rows = p.size(0)
+                    with torch.cuda.device(p.device):
+                        rc = _lib.load().linf_adamw_step(
+                            p.data_ptr(), p.grad.data_ptr(), state["exp_avg"].data_ptr(), state["exp_avg_sq"].data_ptr(),
+                            rows, p.numel() // rows, -1.0 if p_norm is None else float(p_norm), group["lr"], beta1, beta2,
+                            group["eps"], group["weight_decay"], state["step"], torch.cuda.current_stream().cuda_stream)
+                    _lib.check(rc, "adamw_step")
+                    continue
+                self._decay(p, p_norm, group["lr"] * group["weight_decay"], group["eps"])
                 m, v = state["exp_avg"], state["exp_avg_sq"]
                 m.mul_(beta1).add_(p.grad, alpha=1 - beta1)
                 v.mul_(beta2).addcmul_(p.grad, p.grad, value=1 - beta2)

@@ -1,0 +1,161 @@
+// Fused AdamW step with l_p-norm weight decay per weight row (the optimiser of L_inf-dist Net
+// training, adamw.py:30-86 of zbh2047/L_inf-dist-net, which runs it as ~15 elementwise / reduction
+// launches per tensor).  One CTA per row of the [rows, cols] parameter view:
+//   decay  p_norm = inf      : only the entry of largest magnitude shrinks, x_k -= lr*wd * x_k
+//          1 < p_norm < inf  : x_i -= lr*wd * (|x_i| / ||x||_p)^(p-2) * x_i, computed as in the
+//                              reference from s_i = (x_i^2 + eps) / max_j (x_j^2 + eps):
+//                              scale_i = (sum_j s_j^(p/2))^(2/p - 1) * s_i^(p/2 - 1)
+//          p_norm <= 0       : (module without a norm) x_i *= 1 - lr*wd
+//   Adam   m = b1 m + (1-b1) g;  v = b2 v + (1-b2) g^2;
+//          x -= lr / (1 - b1^t) * m / (sqrt(v) / sqrt(1 - b2^t) + eps)
+// The row is read once into shared memory for the reductions; grad, m, v are streamed once.
+// HBM-bound: 16 B read + 12 B written per parameter.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace linf {
+namespace {
+
+struct AdamArgs {
+    float* param; const float* grad; float* m; float* v;
+    int rows, cols;
+    float p_norm;           // +inf, finite > 1, or <= 0 for plain decay
+    float lr_wd;            // lr * weight_decay
+    float beta1, beta2, eps;
+    float step_size;        // lr / (1 - beta1^t)
+    float inv_sqrt_bc2;     // 1 / sqrt(1 - beta2^t)
+};
+
+__device__ __forceinline__ float block_reduce_max(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, s));
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float r = red[0];
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) r = fmaxf(r, red[w]);
+    __syncthreads();
+    return r;
+}
+
+__device__ __forceinline__ float block_reduce_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) v += __shfl_xor_sync(0xffffffffu, v, s);
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float r = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) r += red[w];   // fixed order: reproducible
+    __syncthreads();
+    return r;
+}
+
+// MODE 0: plain decay, 1: p = inf, 2: finite p
+template <int MODE>
+__global__ void __launch_bounds__(256)
+adamw_rows_kernel(const AdamArgs a) {
+    extern __shared__ __align__(16) float row_s[];      // the row of the parameter (MODE > 0)
+    __shared__ float red[8];
+    __shared__ int red_i[8];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const size_t base = (size_t)blockIdx.x * a.cols;
+    float* x = a.param + base;
+
+    int k_star = -1;               // MODE 1: column that decays
+    float coef = 0.f, e_half = 0.f, inv_max = 0.f;   // MODE 2
+    if (MODE == 1) {
+        float best = -1.f; int bi = 0x7fffffff;
+        for (int c = tid; c < a.cols; c += blockDim.x) {
+            const float v = x[c];
+            row_s[c] = v;
+            const float av = fabsf(v);
+            if (av > best) { best = av; bi = c; }
+        }
+#pragma unroll
+        for (int s = 16; s >= 1; s >>= 1) {
+            const float b2 = __shfl_xor_sync(0xffffffffu, best, s);
+            const int i2 = __shfl_xor_sync(0xffffffffu, bi, s);
+            if (b2 > best || (b2 == best && i2 < bi)) { best = b2; bi = i2; }
+        }
+        if (lane == 0) { red[warp] = best; red_i[warp] = bi; }
+        __syncthreads();
+        best = red[0]; bi = red_i[0];
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+            if (red[w] > best || (red[w] == best && red_i[w] < bi)) { best = red[w]; bi = red_i[w]; }
+        k_star = bi;               // lowest index among equal magnitudes
+    } else if (MODE == 2) {
+        float mx = 0.f;
+        for (int c = tid; c < a.cols; c += blockDim.x) {
+            const float v = x[c];
+            row_s[c] = v;
+            mx = fmaxf(mx, v * v + a.eps);
+        }
+        mx = block_reduce_max(mx, red);
+        inv_max = 1.f / mx;
+        e_half = a.p_norm * 0.5f;
+        float sum = 0.f;
+        for (int c = tid; c < a.cols; c += blockDim.x) {
+            const float s = (row_s[c] * row_s[c] + a.eps) * inv_max;
+            sum += powf(s, e_half);                       // s * s^(p/2 - 1)
+        }
+        sum = block_reduce_sum(sum, red);
+        coef = powf(sum, 2.f / a.p_norm - 1.f);
+    }
+    const float one_b1 = 1.f - a.beta1, one_b2 = 1.f - a.beta2;
+    for (int c = tid; c < a.cols; c += blockDim.x) {
+        float xv = (MODE == 0) ? x[c] : row_s[c];
+        if (MODE == 0) xv *= 1.f - a.lr_wd;
+        else if (MODE == 1) { if (c == k_star) xv += -a.lr_wd * xv; }
+        else {
+            const float s = (xv * xv + a.eps) * inv_max;
+            xv = fmaf(-a.lr_wd * coef * powf(s, e_half - 1.f), xv, xv);
+        }
+        const float g = a.grad[base + c];
+        const float m = a.beta1 * a.m[base + c] + one_b1 * g;
+        const float v = a.beta2 * a.v[base + c] + one_b2 * g * g;
+        a.m[base + c] = m;
+        a.v[base + c] = v;
+        const float denom = sqrtf(v) * a.inv_sqrt_bc2 + a.eps;
+        x[c] = xv - a.step_size * (m / denom);
+    }
+}
+
+}  // namespace
+}  // namespace linf
+
+extern "C" int linf_adamw_step(float* param, const float* grad, float* exp_avg, float* exp_avg_sq,
+                               int rows, int cols, float p_norm, float lr, float beta1, float beta2,
+                               float eps, float weight_decay, int step, void* stream) {
+    using namespace linf;
+    if (!param || !grad || !exp_avg || !exp_avg_sq) return LINF_ERR_NULL;
+    if (rows <= 0 || cols <= 0 || step <= 0) return LINF_ERR_DIMS;
+    if (p_norm != p_norm) return LINF_ERR_P;
+    AdamArgs a;
+    a.param = param; a.grad = grad; a.m = exp_avg; a.v = exp_avg_sq;
+    a.rows = rows; a.cols = cols; a.p_norm = p_norm; a.lr_wd = lr * weight_decay;
+    a.beta1 = beta1; a.beta2 = beta2; a.eps = eps;
+    a.step_size = (float)((double)lr / (1.0 - pow((double)beta1, (double)step)));
+    a.inv_sqrt_bc2 = (float)(1.0 / sqrt(1.0 - pow((double)beta2, (double)step)));
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const int mode = !(p_norm > 0.f) ? 0 : (isinf(p_norm) ? 1 : 2);
+    const size_t smem = mode == 0 ? 0 : (size_t)cols * sizeof(float);
+    if (smem > 200 * 1024) return LINF_ERR_TOO_LARGE;
+    // rows of a single element (biases): any rule reduces to the plain decay
+    if (mode == 0 || cols == 1) {
+        if (cols == 1) {
+            // one CTA per 256 rows would idle 255 threads: treat the vector as one row
+            a.rows = 1; a.cols = rows;
+            adamw_rows_kernel<0><<<1, 256, 0, st>>>(a);
+        } else {
+            adamw_rows_kernel<0><<<rows, 256, 0, st>>>(a);
+        }
+    } else if (mode == 1) {
+        if (smem > 48 * 1024 && cudaFuncSetAttribute(adamw_rows_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return LINF_ERR_LAUNCH;
+        adamw_rows_kernel<1><<<rows, 256, smem, st>>>(a);
+    } else {
+        if (smem > 48 * 1024 && cudaFuncSetAttribute(adamw_rows_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return LINF_ERR_LAUNCH;
+        adamw_rows_kernel<2><<<rows, 256, smem, st>>>(a);
+    }
+    return launch_status();
+}

@@ -83,9 +83,10 @@ inf_forward_generic_kernel(const float* __restrict__ x, const float* __restrict_
 // =====================================================================================
 // Geometry of one kernel variant.  A thread owns 8 rows x TN columns; a warp (4 x 8 lanes)
 // owns 32 rows x 8*TN columns; a CTA has 2 warps along m and NT/64 along n.
-template <int NT_, int TN_, int BK_, int MINB_>
+template <int NT_, int TN_, int BK_, int MINB_, int TRK_ = 1>
 struct Geo {
     static constexpr int NT = NT_, TN = TN_, BK = BK_, MINB = MINB_;
+    static constexpr int TRK = TRK_;                    // k-tiles per arg-max tracking step
     static constexpr int BM = 64, BN = (NT / 64) * 8 * TN;
     static constexpr int NOUT = 8 * TN;                 // outputs per thread
     static constexpr int TILE_OUT = BM * BN;
@@ -233,8 +234,9 @@ __device__ __forceinline__ int cid_get(const unsigned (&cid)[H], int e) {
     return (e & 1) ? (int)(cid[e >> 1] >> 16) : (int)(cid[e >> 1] & 0xffffu);
 }
 
-// Finds the first index in k-tile `kt` whose |x - w| equals yv, and the sign there.
-template <int BK>
+// Finds the first index in the TRK k-tiles starting at tile `kt` whose |x - w| equals yv, and the
+// sign there.  (Scanning past the end of a split segment is harmless: a match inside comes first.)
+template <int BK, int TRK>
 __device__ __forceinline__ int resolve_pos(const float* __restrict__ xrow, const float* __restrict__ wrow,
                                            int kt, int K, float yv) {
     if (!(yv > 0.f)) return 0;
@@ -242,7 +244,7 @@ __device__ __forceinline__ int resolve_pos(const float* __restrict__ xrow, const
     int best = 0;
     float tb = 0.f;
 #pragma unroll
-    for (int q = BK / 4 - 1; q >= 0; --q) {
+    for (int q = BK * TRK / 4 - 1; q >= 0; --q) {
         if (kbase + 4 * q < K) {
             const float4 xv = __ldg(reinterpret_cast<const float4*>(xrow + kbase + 4 * q));
             const float4 wv = __ldg(reinterpret_cast<const float4*>(wrow + kbase + 4 * q));
@@ -299,33 +301,44 @@ inf_forward_tiled_kernel(const TiledParams p) {
             cp_async_commit();
         }
         int rd = 0, wr = STAGES - 1;
-        for (int kt = kt0; kt < kt1; kt += 2) {
+        constexpr int TRK = GEO::TRK;
+        for (int kt = kt0; kt < kt1; kt += 2 * TRK) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const int ktc = kt + h;
-                if (ktc < kt1) {
-                    cp_async_wait<STAGES - 2>();
-                    __syncthreads();
-                    if (ktc + STAGES - 1 < kt1)
-                        load_stage<GEO>(smem + wr * STAGE_FLOATS, p, g, m0, n0, ktc + STAGES - 1, tid);
-                    cp_async_commit();
-                    const float* As = smem + rd * STAGE_FLOATS + row_off * GEO::LD;
-                    const float* Bs = smem + rd * STAGE_FLOATS + (BM + col_off) * GEO::LD;
-                    if constexpr (TRACK) {
-                        if (h == 0) {
-                            tile_step<GEO, MODE>(As, Bs, accA, accB);
-                            note_raises<NOUT>(accA, accB, cid, (unsigned)ktc * 0x10001u);
-                        } else {
-                            tile_step<GEO, MODE>(As, Bs, accB, accA);
-                            note_raises<NOUT>(accB, accA, cid, (unsigned)ktc * 0x10001u);
+                const int kb = kt + h * TRK;             // first k-tile of this tracking step
+                if (kb < kt1) {
+#pragma unroll
+                    for (int s2 = 0; s2 < TRK; ++s2) {
+                        const int ktc = kb + s2;
+                        if (ktc < kt1) {
+                            cp_async_wait<STAGES - 2>();
+                            __syncthreads();
+                            if (ktc + STAGES - 1 < kt1)
+                                load_stage<GEO>(smem + wr * STAGE_FLOATS, p, g, m0, n0, ktc + STAGES - 1, tid);
+                            cp_async_commit();
+                            const float* As = smem + rd * STAGE_FLOATS + row_off * GEO::LD;
+                            const float* Bs = smem + rd * STAGE_FLOATS + (BM + col_off) * GEO::LD;
+                            if constexpr (TRACK) {
+                                if (h == 0) {
+                                    if (s2 == 0) tile_step<GEO, MODE>(As, Bs, accA, accB);
+                                    else tile_step<GEO, MODE>(As, Bs, accB, accB);
+                                } else {
+                                    if (s2 == 0) tile_step<GEO, MODE>(As, Bs, accB, accA);
+                                    else tile_step<GEO, MODE>(As, Bs, accA, accA);
+                                }
+                            } else {
+                                tile_step<GEO, MODE>(As, Bs, accA, accA);
+                            }
+                            rd = (rd + 1 == STAGES) ? 0 : rd + 1;
+                            wr = (wr + 1 == STAGES) ? 0 : wr + 1;
                         }
-                    } else {
-                        tile_step<GEO, MODE>(As, Bs, accA, accA);
                     }
-                    rd = (rd + 1 == STAGES) ? 0 : rd + 1;
-                    wr = (wr + 1 == STAGES) ? 0 : wr + 1;
+                    if constexpr (TRACK) {
+                        if (h == 0) note_raises<NOUT>(accA, accB, cid, (unsigned)kb * 0x10001u);
+                        else note_raises<NOUT>(accB, accA, cid, (unsigned)kb * 0x10001u);
+                    }
                 } else if (TRACK && h == 1) {
-                    // odd number of k-tiles: the result sits in the second set
+                    // the last tracking step ended in the second set
                     if constexpr (TRACK) {
 #pragma unroll
                         for (int e = 0; e < NOUT; ++e) accA[e] = accB[e];
@@ -406,7 +419,7 @@ inf_forward_tiled_kernel(const TiledParams p) {
                             p.y[o] = yv;
                             if constexpr (TRACK) {
                                 const float* wrow = p.w + ((size_t)g * p.N + n) * p.K;
-                                p.pos[o] = resolve_pos<BK>(xrow, wrow, cid_get(cid, i * TN + j), p.K, yv);
+                                p.pos[o] = resolve_pos<BK, GEO::TRK>(xrow, wrow, cid_get(cid, i * TN + j), p.K, yv);
                             }
                         }
                     }
@@ -444,6 +457,7 @@ const Variant kVariants[] = {
     make_variant<Geo<128, 4, 16, 3>, 1>(),   // 7: as 2 with scalar sub + 3-input max
     make_variant<Geo<128, 4, 32, 3>, 2>(),   // 8: as 2 with 32-wide k-tiles
     make_variant<Geo<128, 4, 8, 3>, 2>(),    // 9: as 2 with 8-wide k-tiles
+    make_variant<Geo<128, 4, 16, 3, 2>, 2>(), // 10: as 2, arg-max tracked every second k-tile (long rows)
 };
 constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
 
@@ -467,12 +481,16 @@ static int tiled_tiles(const Dims& d, const Variant& v) {
 }
 
 // Splitting k-tiles across CTAs pays when whole tiles would leave a large part of the last
-// wave of CTAs idle.
+// wave of CTAs idle -- unless the rows are short: every CTA of a split launch ends with a merge
+// and an arg-max rescan at the same moment, which costs more than the idle part of a wave when
+// the k loop itself is short (measured: 217 us split vs 209 us unsplit at K = 784, 956 us vs
+// 1063 us at K = 5120).  With fewer tiles than CTA slots there is nothing to lose: split.
 static bool want_split(const Dims& d, const Variant& v) {
     const int slots = v.min_blocks * sm_count();
     const int tiles = tiled_tiles(d, v);
     const int waves = (tiles + slots - 1) / slots;
-    return (double)tiles / ((double)waves * slots) < 0.9;
+    if ((double)tiles / ((double)waves * slots) >= 0.9) return false;
+    return tiles < slots || d.CIg >= 1536;
 }
 
 size_t inf_forward_workspace(const Dims& d) {

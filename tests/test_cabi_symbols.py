@@ -47,8 +47,10 @@ def test_error_codes_without_gpu(lib):
 
 
 def test_workspace_query(lib):
-    # config-1 shape: 8 x 40 = 320 tiles on 296 CTA slots leaves most of a wave idle -> split
-    assert lib.linf_inf_dist_forward_workspace_bytes(512, 5120, 784, 1, 1) > 0
+    # 640 tiles on 444 CTA slots leave most of the second wave idle: long rows are split over k
+    assert lib.linf_inf_dist_forward_workspace_bytes(512, 5120, 5120, 1, 1) > 0
+    # fewer tiles than CTA slots: split as well
+    assert lib.linf_inf_dist_forward_workspace_bytes(64, 256, 784, 1, 1) > 0
     # conv-shaped and tiny problems take the generic path: no scratch
     assert lib.linf_inf_dist_forward_workspace_bytes(8, 16, 27, 1, 9) == 0
     assert lib.linf_inf_dist_forward_workspace_bytes(0, 16, 27, 1, 9) == 0
