@@ -166,7 +166,11 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        # collectives on a high-priority stream: their few CTAs are placed ahead of the queued CTAs
+        # of the optimiser / scatter kernels instead of waiting for those grids to drain
+        opts = dist.ProcessGroupNCCL.Options()
+        opts.is_high_priority_stream = True
+        dist.init_process_group("nccl", device_id=dev, pg_options=opts)
     lib = _lib.load()
     L.set_backward_mode(args.backward)
 

@@ -49,33 +49,46 @@ class AdamW(Optimizer):
             with torch.enable_grad():
                 loss = closure()
         for group in self.param_groups:
-            beta1, beta2 = group["betas"]
             for p in group["params"]:
-                if p.grad is None:
-                    continue
-                if p.grad.is_sparse:
-                    raise RuntimeError("AdamW does not support sparse gradients")
-                state = self.state[p]
-                if not state:
-                    state["step"] = 0
-                    state["exp_avg"] = torch.zeros_like(p, memory_format=torch.preserve_format)
-                    state["exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.preserve_format)
-                state["step"] += 1
-                p_norm = get_p_norm(group["module"])
-                if self._fused_ok(p):
-                    # CUDA tensors: one fused launch per tensor (csrc/adamw.cu)
-                    rows = p.size(0)
-                    with torch.cuda.device(p.device):
-                        rc = _lib.load().linf_adamw_step(
-                            p.data_ptr(), p.grad.data_ptr(), state["exp_avg"].data_ptr(), state["exp_avg_sq"].data_ptr(),
-                            rows, p.numel() // rows, -1.0 if p_norm is None else float(p_norm), group["lr"], beta1, beta2,
-                            group["eps"], group["weight_decay"], state["step"], torch.cuda.current_stream().cuda_stream)
-                    _lib.check(rc, "adamw_step")
-                    continue
-                self._decay(p, p_norm, group["lr"] * group["weight_decay"], group["eps"])
-                m, v = state["exp_avg"], state["exp_avg_sq"]
-                m.mul_(beta1).add_(p.grad, alpha=1 - beta1)
-                v.mul_(beta2).addcmul_(p.grad, p.grad, value=1 - beta2)
-                denom = (v.sqrt() / math.sqrt(1 - beta2 ** state["step"])).add_(group["eps"])
-                p.addcdiv_(m, denom, value=-group["lr"] / (1 - beta1 ** state["step"]))
+                if p.grad is not None:
+                    self._update(p, group)
         return loss
+
+    @torch.no_grad()
+    def step_params(self, params):
+        """Updates only the given parameters (each at most once per call).  Lets a data-parallel
+        driver run the optimiser for one gradient bucket as soon as that bucket is reduced, while
+        the remaining buckets are still in flight."""
+        if not hasattr(self, "_group_of"):
+            self._group_of = {id(q): g for g in self.param_groups for q in g["params"]}
+        for p in params:
+            if p.grad is not None:
+                self._update(p, self._group_of[id(p)])
+
+    def _update(self, p, group):
+        if p.grad.is_sparse:
+            raise RuntimeError("AdamW does not support sparse gradients")
+        beta1, beta2 = group["betas"]
+        state = self.state[p]
+        if not state:
+            state["step"] = 0
+            state["exp_avg"] = torch.zeros_like(p, memory_format=torch.preserve_format)
+            state["exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.preserve_format)
+        state["step"] += 1
+        p_norm = get_p_norm(group["module"])
+        if self._fused_ok(p):
+            # CUDA tensors: one fused launch per tensor (csrc/adamw.cu)
+            rows = p.size(0)
+            with torch.cuda.device(p.device):
+                rc = _lib.load().linf_adamw_step(
+                    p.data_ptr(), p.grad.data_ptr(), state["exp_avg"].data_ptr(), state["exp_avg_sq"].data_ptr(),
+                    rows, p.numel() // rows, -1.0 if p_norm is None else float(p_norm), group["lr"], beta1, beta2,
+                    group["eps"], group["weight_decay"], state["step"], torch.cuda.current_stream().cuda_stream)
+            _lib.check(rc, "adamw_step")
+            return
+        self._decay(p, p_norm, group["lr"] * group["weight_decay"], group["eps"])
+        m, v = state["exp_avg"], state["exp_avg_sq"]
+        m.mul_(beta1).add_(p.grad, alpha=1 - beta1)
+        v.mul_(beta2).addcmul_(p.grad, p.grad, value=1 - beta2)
+        denom = (v.sqrt() / math.sqrt(1 - beta2 ** state["step"])).add_(group["eps"])
+        p.addcdiv_(m, denom, value=-group["lr"] / (1 - beta1 ** state["step"]))

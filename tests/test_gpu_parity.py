@@ -286,3 +286,36 @@ def test_fused_adamw_matches_torch_rule(cuda, lib, p_norm):
         oc.step(); og.step()
     for prm_c, prm_g in zip(cpu.parameters(), gpu.parameters()):
         torch.testing.assert_close(prm_g.detach().cpu(), prm_c.detach(), rtol=2e-5, atol=2e-6)
+
+
+def test_pipelined_step_equals_plain_step(cuda, lib):
+    """The hand-scheduled step (optimiser on a side stream, forward waiting per layer) must leave
+    exactly the parameters that forward -> backward -> optimizer.step() leaves."""
+    import linfdist_b200 as L
+    from linfdist_b200.train_step import DataParallelStep, MarginLoss, hinge
+
+    def run(pipelined):
+        torch.manual_seed(3)
+        net = L.Model(L.MLP(3, 1, (3, 8, 8), num_classes=10), L.BoundFinalIdentity(), eps=8 / 255).cuda()
+        L.set_p_norm(net, float("inf"))
+        opt = L.AdamW(net, lr=0.02, betas=(0.9, 0.99), eps=1e-10, weight_decay=5e-3)
+        model = DataParallelStep(net, opt) if pipelined else net
+        loss_fn = MarginLoss(hinge(0.75), 1.0)
+        gen = torch.Generator().manual_seed(5)
+        for _ in range(4):
+            x = torch.rand(64, 3, 8, 8, generator=gen).cuda(); t = torch.randint(0, 10, (64,), generator=gen).cuda()
+            out, worst = model(x, targets=t)
+            loss = loss_fn(out, worst, t)
+            opt.zero_grad(set_to_none=True)
+            loss.backward()
+            if pipelined:
+                model.finish_step()
+            else:
+                opt.step()
+        if pipelined:
+            model.synchronize()
+        torch.cuda.synchronize()
+        return [p.detach().clone() for p in net.parameters()]
+
+    for a, b in zip(run(False), run(True)):
+        assert torch.equal(a, b)

@@ -198,7 +198,7 @@ def test_train_step_decreases_loss_on_cpu(monkeypatch):
     assert losses[-1] < losses[0]
 
 
-def _ddp_worker(rank, world, port, out):
+def _ddp_worker(rank, world, port, out, overlapped):
     import torch.distributed as dist
     os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -209,36 +209,53 @@ def _ddp_worker(rank, world, port, out):
     torch.manual_seed(7)                               # same initial weights on every rank
     net = L.Model(L.MLP(2, 1, (1, 3, 3), num_classes=3), L.BoundFinalIdentity(), eps=0.01)
     L.set_p_norm(net, float("inf"))
-    ddp = nn.parallel.DistributedDataParallel(net)
     opt = L.AdamW(net, lr=0.05, betas=(0.9, 0.99), eps=1e-10, weight_decay=1e-3)
+    if overlapped:
+        from linfdist_b200.train_step import DataParallelStep
+        ddp = DataParallelStep(net, opt)               # all-reduce + optimiser per parameter inside backward
+    else:
+        ddp = nn.parallel.DistributedDataParallel(net)
     gen = torch.Generator().manual_seed(100 + rank)    # every rank its own batch shard
     x = torch.rand(8, 1, 3, 3, generator=gen); t = torch.randint(0, 3, (8,), generator=gen)
     loss_fn = MarginLoss(hinge(0.75), kappa=1.0)
     for _ in range(2):
         o, wst = ddp(x, targets=t)
         loss = loss_fn(o, wst, t)
-        opt.zero_grad(); loss.backward(); opt.step()
+        opt.zero_grad(set_to_none=True); loss.backward()
+        if not overlapped:
+            opt.step()
+        else:
+            ddp.finish_step(); ddp.synchronize()
     flat = torch.cat([p.detach().flatten() for p in net.parameters()])
     gathered = [torch.zeros_like(flat) for _ in range(world)]
     dist.all_gather(gathered, flat)
     if rank == 0:
-        out.put(bool(all(torch.equal(gathered[0], g) for g in gathered)))
+        out.put((bool(all(torch.equal(gathered[0], g) for g in gathered)), gathered[0]))
     dist.destroy_process_group()
 
 
-def test_data_parallel_two_ranks_gloo():
-    """Two CPU ranks, different batch shards, DDP gradient all-reduce: parameters stay identical."""
+def _run_two_ranks(overlapped):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
-    port = 29500 + (os.getpid() % 500)
-    procs = [ctx.Process(target=_ddp_worker, args=(r, 2, port, out)) for r in range(2)]
+    port = 29500 + (os.getpid() % 400) + (50 if overlapped else 0)
+    procs = [ctx.Process(target=_ddp_worker, args=(r, 2, port, out, overlapped)) for r in range(2)]
     for p in procs:
         p.start()
+    same, params = out.get(timeout=240)
     for p in procs:
-        p.join(timeout=180)
+        p.join(timeout=60)
         assert p.exitcode == 0
-    assert out.get(timeout=5) is True
+    assert same is True
+    return params
+
+
+def test_data_parallel_two_ranks_gloo():
+    """Two CPU ranks, different batch shards: parameters stay identical across ranks, and applying
+    the optimiser parameter by parameter inside backward gives what a plain DDP step gives."""
+    plain = _run_two_ranks(False)
+    overlapped = _run_two_ranks(True)
+    assert torch.allclose(plain, overlapped, rtol=1e-6, atol=1e-7)
 
 
 def test_bench_sharding_inputs():
