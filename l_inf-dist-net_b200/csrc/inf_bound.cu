@@ -82,10 +82,10 @@ inf_bound_generic_kernel(const float* __restrict__ xl, const float* __restrict__
 }
 
 // ------------------------------------------------------------------------------------
-// tiled path (HW == 1, CI/G % 4 == 0, 16-byte aligned): 64 x 128 tile, 128 threads,
-// 8 x 8 outputs (x 2 bounds) per thread, cp.async ring, 2 CTAs per SM.
+// tiled path (HW == 1, CI/G % 4 == 0, 16-byte aligned): 64 x 64 tile, 128 threads,
+// 8 x 4 outputs (x 2 bounds) per thread, cp.async ring, 3 CTAs per SM.
 // ------------------------------------------------------------------------------------
-constexpr int BM = 64, BN = 128, NT = 128, BK = 16, LD = BK + 4, STAGES = 4;
+constexpr int BM = 64, BN = 64, NT = 128, BK = 16, LD = BK + 4, STAGES = 4, TN = 4, NO = 8 * TN;
 constexpr int STAGE_FLOATS = (2 * BM + BN) * LD;
 constexpr int SMEM_BYTES = STAGES * STAGE_FLOATS * 4;
 
@@ -125,39 +125,39 @@ __device__ __forceinline__ void load_stage(float* stage, const BoundParams& p, i
 // !FAST: literal rule, accL = running lower bound.
 template <bool FAST>
 __device__ __forceinline__ void tile_step(const float* __restrict__ Ls, const float* __restrict__ Us,
-                                          const float* __restrict__ Bs, float (&accL)[64], float (&accU)[64]) {
+                                          const float* __restrict__ Bs, float (&accL)[NO], float (&accU)[NO]) {
 #pragma unroll
     for (int k4 = 0; k4 < BK / 4; ++k4) {
-        ulonglong2 bf[8];
+        ulonglong2 bf[TN];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) bf[j] = *reinterpret_cast<const ulonglong2*>(Bs + (8 * j) * LD + k4 * 4);
+        for (int j = 0; j < TN; ++j) bf[j] = *reinterpret_cast<const ulonglong2*>(Bs + (8 * j) * LD + k4 * 4);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const ulonglong2 al = *reinterpret_cast<const ulonglong2*>(Ls + (4 * i) * LD + k4 * 4);
             const ulonglong2 au = *reinterpret_cast<const ulonglong2*>(Us + (4 * i) * LD + k4 * 4);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < TN; ++j) {
                 if (FAST) {
                     float n0, n1, n2, n3, u0, u1, u2, u3;
                     unpack_f32x2(sub_f32x2(bf[j].x, al.x), n0, n1);   // w - lower
                     unpack_f32x2(sub_f32x2(bf[j].y, al.y), n2, n3);
                     unpack_f32x2(sub_f32x2(au.x, bf[j].x), u0, u1);   // upper - w
                     unpack_f32x2(sub_f32x2(au.y, bf[j].y), u2, u3);
-                    float U = accU[i * 8 + j], L = accL[i * 8 + j];
+                    float U = accU[i * TN + j], L = accL[i * TN + j];
                     U = max3(U, n0, u0); L = min3(L, n0, u0);
                     U = max3(U, n1, u1); L = min3(L, n1, u1);
                     U = max3(U, n2, u2); L = min3(L, n2, u2);
                     U = max3(U, n3, u3); L = min3(L, n3, u3);
-                    accU[i * 8 + j] = U; accL[i * 8 + j] = L;
+                    accU[i * TN + j] = U; accL[i * TN + j] = L;
                 } else {
                     float l0, l1, l2, l3, u0, u1, u2, u3, w0, w1, w2, w3;
                     unpack_f32x2(al.x, l0, l1); unpack_f32x2(al.y, l2, l3);
                     unpack_f32x2(au.x, u0, u1); unpack_f32x2(au.y, u2, u3);
                     unpack_f32x2(bf[j].x, w0, w1); unpack_f32x2(bf[j].y, w2, w3);
-                    literal_term(l0, u0, w0, accL[i * 8 + j], accU[i * 8 + j]);
-                    literal_term(l1, u1, w1, accL[i * 8 + j], accU[i * 8 + j]);
-                    literal_term(l2, u2, w2, accL[i * 8 + j], accU[i * 8 + j]);
-                    literal_term(l3, u3, w3, accL[i * 8 + j], accU[i * 8 + j]);
+                    literal_term(l0, u0, w0, accL[i * TN + j], accU[i * TN + j]);
+                    literal_term(l1, u1, w1, accL[i * TN + j], accU[i * TN + j]);
+                    literal_term(l2, u2, w2, accL[i * TN + j], accU[i * TN + j]);
+                    literal_term(l3, u3, w3, accL[i * TN + j], accU[i * TN + j]);
                 }
             }
         }
@@ -169,10 +169,10 @@ __device__ __forceinline__ void tile_step(const float* __restrict__ Ls, const fl
 template <bool FAST>
 __device__ __forceinline__ bool run_tile(float* smem, const BoundParams& p, int g, int m0, int n0,
                                          int tid, int row_off, int col_off,
-                                         float (&accL)[64], float (&accU)[64]) {
+                                         float (&accL)[NO], float (&accU)[NO]) {
     bool bad = false;
 #pragma unroll
-    for (int e = 0; e < 64; ++e) { accL[e] = 0.f; accU[e] = 0.f; }
+    for (int e = 0; e < NO; ++e) { accL[e] = 0.f; accU[e] = 0.f; }
     __syncthreads();
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
@@ -208,24 +208,24 @@ __device__ __forceinline__ bool run_tile(float* smem, const BoundParams& p, int 
     return bad;
 }
 
-__global__ void __launch_bounds__(NT, 2)
+__global__ void __launch_bounds__(NT, 3)
 inf_bound_tiled_kernel(const BoundParams p) {
     extern __shared__ __align__(16) float smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int wm = warp & 1, wn = warp >> 1, lm = lane >> 3, ln = lane & 7;
-    const int row_off = wm * 32 + lm, col_off = wn * 64 + ln;
+    const int row_off = wm * 32 + lm, col_off = wn * (8 * TN) + ln;
 
     const int tiles_per_group = p.tiles_m * p.tiles_n;
     const int tile = blockIdx.x;
     const int g = tile / tiles_per_group, tg = tile - g * tiles_per_group;
     const int n0 = (tg / p.tiles_m) * BN, m0 = (tg % p.tiles_m) * BM;
 
-    float accL[64], accU[64];
+    float accL[NO], accU[NO];
     const bool bad = run_tile<true>(smem, p, g, m0, n0, tid, row_off, col_off, accL, accU);
     const bool any_bad = __syncthreads_or(bad);
     if (!any_bad) {
 #pragma unroll
-        for (int e = 0; e < 64; ++e) accL[e] = 0.f - accL[e];
+        for (int e = 0; e < NO; ++e) accL[e] = 0.f - accL[e];
     } else {
         run_tile<false>(smem, p, g, m0, n0, tid, row_off, col_off, accL, accU);
     }
@@ -234,12 +234,12 @@ inf_bound_tiled_kernel(const BoundParams p) {
         const int m = m0 + row_off + 4 * i;
         if (m < p.M) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < TN; ++j) {
                 const int n = n0 + col_off + 8 * j;
                 if (n < p.N) {
                     const size_t o = (size_t)m * p.ldo + (size_t)g * p.N + n;
-                    p.yl[o] = accL[i * 8 + j];
-                    p.yu[o] = accU[i * 8 + j];
+                    p.yl[o] = accL[i * TN + j];
+                    p.yu[o] = accU[i * TN + j];
                 }
             }
         }
