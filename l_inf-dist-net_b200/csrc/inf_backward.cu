@@ -4,27 +4,24 @@
 //   grad_weight[o, idx]             -= s * g      g = grad_output[b, o, hw], idx = pos & 0x7fffffff
 //
 // Ordered kernels (the default): every destination ROW -- a (b, group, hw) row of grad_input or
-// an output-channel row of grad_weight -- is produced by one group of warps as a stable
+// an output-channel row of grad_weight -- is produced by one group of threads as a stable
 // counting sort followed by per-bin sequential sums, all in shared memory:
-//   0. (sparse rows only: fewer sources than bins, as for grad_weight) a bitmap of the bins
-//      that occur turns bin indices into dense ids, so that the work below scales with the
-//      number of sources, not with the row length; the row is zero-filled up front;
-//   1. histogram of the row's (dense) bin ids (integer atomics; each warp of the group counts
-//      its own contiguous range of sources);
-//   2. exclusive scan -> first slot of every bin, and of every warp's share inside the bin;
-//   3. stable placement: the warps walk their ranges 32 sources at a time in ascending order;
-//      lanes that hit the same bin get consecutive slots in lane order (match_any + popc);
+//   1. histogram of the row's bin indices;
+//   2. exclusive scan -> first slot of every bin;
+//   3. placement of every (signed) gradient value into the next free slot of its bin, in
+//      ascending source order;
 //   4. one thread per bin adds the bin's values one by one, in slot (= source) order, from +0,
-//      and writes the result (dense rows are written out whole: no zero fill needed).
+//      and the finished row is written out whole (no zero fill of the destination needed).
 // Every bin therefore sees sequential fp32 adds in ascending source order: a fixed,
 // reproducible order, and one of the orders the reference's atomicAdd scatter can produce.
+// Two implementations: inf_backward_rows_kernel keeps the row's sources in registers (rows that
+// fit their thread group: the dense-layer shapes); inf_backward_ordered_kernel is the general
+// one (any row length, sparse rows through a bitmap of occurring bins, conv-shaped tensors).
 //
 // Atomic kernel: one pass over (grad_output, pos) produces both gradients with fp32 atomics;
 // for grad_weight a 32 x 32 tile is transposed through shared memory so that the lanes of a
 // warp run over the batch for one output channel, equal bins are combined inside the warp and
 // one atomic is issued per distinct bin.
-#include <cstdio>
-
 #include "common.cuh"
 
 namespace linf {
@@ -139,10 +136,8 @@ inf_backward_ordered_kernel(const float* __restrict__ gout, const int* __restric
         for (int q = threadIdx.x; q < total; q += blockDim.x) {
             const int j = q % rpc, e = q / rpc;
             if (row0 + j < n_rows) {
-                const int oj = o - (CTA_ROW ? 0 : warp) + j;              // same group: rows of a CTA are
-                const int rowj = row0 + j;                                // consecutive, recompute g, o
+                const int rowj = row0 + j;                                // rows of a CTA may straddle groups
                 const int gj = rowj / d.COg, ojj = rowj - gj * d.COg;
-                (void)oj;
                 size_t a;
                 if (HW == 1) a = (size_t)e * d.CO + (size_t)gj * d.COg + ojj;
                 else { const int b = e / HW, hw = e - b * HW; a = ((size_t)(b * d.G + gj) * d.COg + ojj) * HW + hw; }
@@ -167,13 +162,6 @@ inf_backward_ordered_kernel(const float* __restrict__ gout, const int* __restric
     const int e_begin = gwp * per_warp, e_end = min(n_src, e_begin + per_warp);
     constexpr int U = 4;                                 // 32-source batches fetched together
 
-#ifdef LINF_PHASE_TIMERS
-    long long tph[8]; int nph = 0;
-#define LINF_STAMP() do { tph[nph++] = clock64(); } while (0)
-#else
-#define LINF_STAMP() do {} while (0)
-#endif
-    LINF_STAMP();
     int D = nb;
     if (COMPACT) {
         // ---- 0. which bins occur; zero-fill the destination row ----
@@ -201,7 +189,6 @@ inf_backward_ordered_kernel(const float* __restrict__ gout, const int* __restric
         group_exclusive_scan<CTA_ROW>(wp, nbw, gt, GS, lane, gwp, wsum);
         D = wp[nbw];
     }
-    LINF_STAMP();
     // ---- 1. histogram of dense ids, per warp of the group ----
     for (int w = 0; w < W; ++w)
         for (int i = gt; i < D; i += GS) hist[w * DM + i] = 0;
@@ -221,7 +208,6 @@ inf_backward_ordered_kernel(const float* __restrict__ gout, const int* __restric
         }
     }
     sync();
-    LINF_STAMP();
     // ---- 2. scans: offsets of the warps inside each bin, then first slot of each bin ----
     for (int i = gt; i < D; i += GS) {
         int run = 0;
@@ -233,7 +219,6 @@ inf_backward_ordered_kernel(const float* __restrict__ gout, const int* __restric
     for (int w = 0; w < W; ++w)
         for (int i = gt; i < D; i += GS) hist[w * DM + i] += seg[i];
     sync();
-    LINF_STAMP();
     // ---- 3. stable placement ----
     for (int eb = e_begin; eb < e_end; eb += 32 * U) {
         int pv[U]; float gv[U];
@@ -275,7 +260,6 @@ inf_backward_ordered_kernel(const float* __restrict__ gout, const int* __restric
         }
     }
     sync();
-    LINF_STAMP();
     // ---- 4. per-bin sequential sums ----
     for (int i = gt; i < D; i += GS) {
         float acc = 0.f;
@@ -295,13 +279,6 @@ inf_backward_ordered_kernel(const float* __restrict__ gout, const int* __restric
         for (int j = s0; j < s1; ++j) acc += sorted[j];
         dst[d_base + (size_t)(COMPACT ? keys[i] : i) * d_step] = acc;
     }
-    LINF_STAMP();
-#ifdef LINF_PHASE_TIMERS
-    if (blockIdx.x == 7 && threadIdx.x == 0)
-        printf("mode %d cta_row %d compact %d staged %d: zero+bitmap %lld hist %lld scan %lld place %lld sums %lld cycles\n",
-               MODE, (int)CTA_ROW, (int)COMPACT, (int)STAGED, tph[1] - tph[0], tph[2] - tph[1], tph[3] - tph[2],
-               tph[4] - tph[3], tph[5] - tph[4]);
-#endif
 }
 
 // --------------------------------------------------------------------------------------------
@@ -351,13 +328,6 @@ inf_backward_rows_kernel(const float* __restrict__ gout, const int* __restrict__
     float* sorted = reinterpret_cast<float*>(wsum + 32); // [n_src]
     unsigned short* skey = reinterpret_cast<unsigned short*>(sorted + n_src);   // [n_src] source index of a slot
 
-#ifdef LINF_PHASE_TIMERS
-    long long tq[8]; int nq = 0;
-#define LINF_STAMP2() do { tq[nq++] = clock64(); } while (0)
-#else
-#define LINF_STAMP2() do {} while (0)
-#endif
-    LINF_STAMP2();
     int pv[EPT]; float gv[EPT];
     if (CTA_ROW) {
         size_t s_base; int s_step;
@@ -430,8 +400,6 @@ inf_backward_rows_kernel(const float* __restrict__ gout, const int* __restrict__
         d_base = (size_t)row * d.CIg; d_step = 1;
     }
 
-    if (pv[0] == 0x12345678) dst[0] = gv[EPT - 1];
-    LINF_STAMP2();
     // ---- 1. histogram ----
     for (int i = gt; i < C * (nb + 1); i += GS) hist[i] = 0;
     sync();
@@ -441,7 +409,6 @@ inf_backward_rows_kernel(const float* __restrict__ gout, const int* __restrict__
         if (idx < nb) atomicAdd(&myhist[idx], 1);        // an index outside the group is dropped
     }
     sync();
-    LINF_STAMP2();
     // ---- 2. first slot of every bin (and of every copy's share of the bin) ----
     if (C > 1) {
         for (int i = gt; i < nb; i += GS) {
@@ -458,7 +425,6 @@ inf_backward_rows_kernel(const float* __restrict__ gout, const int* __restrict__
         for (int i = gt; i <= nb; i += GS) seg[i] = hist[i];
     }
     sync();
-    LINF_STAMP2();
     // ---- 3. placement: value and source index into the next free slot of the bin ----
 #pragma unroll
     for (int j = 0; j < EPT; ++j) {
@@ -513,7 +479,6 @@ inf_backward_rows_kernel(const float* __restrict__ gout, const int* __restrict__
         }
     }
     sync();
-    LINF_STAMP2();
     // ---- 4. per bin: ascending source order, then sequential fp32 adds from +0 ----
     if (CTA_ROW) {
         // First pass: one thread per bin adds in slot order while checking that the source indices
@@ -566,13 +531,6 @@ inf_backward_rows_kernel(const float* __restrict__ gout, const int* __restrict__
             dst[d_base + (size_t)i * d_step] = acc;
         }
     }
-    LINF_STAMP2();
-#ifdef LINF_PHASE_TIMERS
-    if (blockIdx.x == 7 && threadIdx.x == 0)
-        printf("fast mode %d cta_row %d ept %d: load %lld hist %lld scan %lld place %lld sums %lld cycles, relisted bins %d\n",
-               MODE, (int)CTA_ROW, EPT, tq[1] - tq[0], tq[2] - tq[1], tq[3] - tq[2], tq[4] - tq[3], tq[5] - tq[4],
-               CTA_ROW ? wsum[24] : -1);
-#endif
 }
 
 // Both gradients with atomics; tile = 32 rows (r) x 32 output channels of one group.

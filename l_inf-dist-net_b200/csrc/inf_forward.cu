@@ -1,20 +1,23 @@
 // inf-dist forward: y[r,o] = max_i |x[r,i] - w[o,i]| with capture of the lowest arg-max index.
 //
-// Two paths:
-//   * tiled path (dense layers: HW == 1, CI/G a multiple of 4, 16-byte aligned pointers):
-//     a register-tiled (max, |a-b|) "GEMM" on the FP32 cores.  A CTA of 128 threads owns a
-//     64 x 128 output tile, a thread an 8 x 8 sub-tile.  Operand tiles are staged through
-//     shared memory with cp.async in a multi-stage ring and read back with 128-bit loads
-//     along k, so that two neighbouring k-terms of one output sit in one 64-bit register
-//     pair: one packed `sub.f32x2` produces both differences and one 3-input `max.f32`
-//     folds both |differences| into the running maximum (one issue slot per term).
+// Three paths:
+//   * tiled path (dense layers: HW == 1, CI/G a multiple of 4, 16-byte aligned pointers, at
+//     least 32 outputs per group): a register-tiled (max, |a-b|) "GEMM" on the FP32 cores.  A
+//     CTA of 128 threads owns a 64 x 64 output tile, a thread an 8 x 4 sub-tile, three CTAs share
+//     an SM.  Operand tiles are staged through shared memory with cp.async in a 4-stage ring and
+//     read back with 128-bit loads along k, so that two neighbouring k-terms of one output sit in
+//     one 64-bit register pair: one packed `sub.f32x2` produces both differences and one 3-input
+//     `max.f32` folds both |differences| into the running maximum.  Both are half-rate
+//     instructions, i.e. two issue cycles per pair of terms each -- the same two cycles per term
+//     as a scalar subtract plus a scalar max, but with half the instructions to fetch and decode.
 //     The arg-max is NOT tracked per term.  The loop only records, once per k-tile, which
 //     k-tile last raised the maximum; after the loop the winning k-tile alone is rescanned
 //     for the first index whose |difference| equals the maximum (strict ">" between tiles
 //     plus first-match inside a tile = lowest index among exact ties).
-//     With scratch memory the k-tiles of all output tiles are dealt out evenly to
-//     2 CTAs per SM; an output tile cut by a CTA boundary is finished by whichever of its
+//     With scratch memory the k-tiles of all output tiles are dealt out evenly to the CTAs that
+//     fit the GPU at once; an output tile cut by a CTA boundary is finished by whichever of its
 //     CTAs arrives last (ticket counter, nobody waits).
+//   * few outputs per group (skinny.cu): the reduction is spread over the threads of a CTA.
 //   * generic path (any G, HW, alignment): 32 x 32 tile, index tracked per term.
 #include "common.cuh"
 
@@ -154,34 +157,6 @@ __device__ __forceinline__ void tile_step(const float* __restrict__ As, const fl
 #pragma unroll
         for (int j = 0; j < TN; ++j)
             bf[j] = *reinterpret_cast<const ulonglong2*>(Bs + (8 * j) * LD + k4 * 4);
-        if (MODE == 3) {
-            // software-pipelined order: the packed subtractions of row i+1 are written between
-            // the 3-input maxima of row i, so that FMA-pipe and ALU-pipe instructions alternate
-            unsigned long long dc[TN][2], dn[TN][2];
-            {
-                const ulonglong2 af = *reinterpret_cast<const ulonglong2*>(As + k4 * 4);
-#pragma unroll
-                for (int j = 0; j < TN; ++j) { dc[j][0] = sub_f32x2(af.x, bf[j].x); dc[j][1] = sub_f32x2(af.y, bf[j].y); }
-            }
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                ulonglong2 af = make_ulonglong2(0, 0);
-                if (i < 7) af = *reinterpret_cast<const ulonglong2*>(As + (4 * (i + 1)) * LD + k4 * 4);
-#pragma unroll
-                for (int j = 0; j < TN; ++j) {
-                    if (i < 7) { dn[j][0] = sub_f32x2(af.x, bf[j].x); dn[j][1] = sub_f32x2(af.y, bf[j].y); }
-                    float a = (k4 == 0) ? in[i * TN + j] : out[i * TN + j];
-                    float t0, t1, t2, t3;
-                    unpack_f32x2(dc[j][0], t0, t1); unpack_f32x2(dc[j][1], t2, t3);
-                    a = max3(a, fabsf(t0), fabsf(t1));
-                    a = max3(a, fabsf(t2), fabsf(t3));
-                    out[i * TN + j] = a;
-                }
-#pragma unroll
-                for (int j = 0; j < TN; ++j) { dc[j][0] = dn[j][0]; dc[j][1] = dn[j][1]; }
-            }
-            continue;
-        }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const ulonglong2 af = *reinterpret_cast<const ulonglong2*>(As + (4 * i) * LD + k4 * 4);
@@ -447,17 +422,11 @@ constexpr Variant make_variant() {
 }
 
 const Variant kVariants[] = {
-    make_variant<Geo<256, 4, 16, 2>, 2>(),   // 0: 8x4 per thread, 256 threads, 2 CTAs/SM
-    make_variant<Geo<128, 8, 16, 2>, 2>(),   // 1: 8x8 per thread, 128 threads, 2 CTAs/SM
+    make_variant<Geo<256, 4, 16, 2>, 2>(),   // 0: 8x4 per thread, 256 threads (64x128 tile), 2 CTAs/SM
+    make_variant<Geo<128, 8, 16, 2>, 2>(),   // 1: 8x8 per thread, 128 threads (64x128 tile), 2 CTAs/SM
     make_variant<Geo<128, 4, 16, 3>, 2>(),   // 2: 8x4 per thread, 128 threads (64x64 tile), 3 CTAs/SM (default)
-    make_variant<Geo<256, 4, 16, 2>, 0>(),   // 3: as 0 with scalar sub + 2-input max
-    make_variant<Geo<128, 4, 16, 4>, 2>(),   // 4: 8x4 per thread, 128 threads, 4 CTAs/SM
-    make_variant<Geo<256, 4, 32, 2>, 2>(),   // 5: as 0 with 32-wide k-tiles
-    make_variant<Geo<128, 4, 16, 3>, 3>(),   // 6: as 2, subtractions and maxima interleaved in source order
-    make_variant<Geo<128, 4, 16, 3>, 1>(),   // 7: as 2 with scalar sub + 3-input max
-    make_variant<Geo<128, 4, 32, 3>, 2>(),   // 8: as 2 with 32-wide k-tiles
-    make_variant<Geo<128, 4, 8, 3>, 2>(),    // 9: as 2 with 8-wide k-tiles
-    make_variant<Geo<128, 4, 16, 3, 2>, 2>(), // 10: as 2, arg-max tracked every second k-tile (long rows)
+    make_variant<Geo<128, 4, 16, 3>, 0>(),   // 3: as 2 with scalar subtract + 2-input max
+    make_variant<Geo<128, 4, 16, 3>, 1>(),   // 4: as 2 with scalar subtract + 3-input max
 };
 constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
 

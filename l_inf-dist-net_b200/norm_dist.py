@@ -63,6 +63,26 @@ def _shape5(x, weight, group):
     return x.size(0), weight.size(0), x.size(1), group, x.size(2)
 
 
+def _rows_view(t):
+    """[B, C, HW] -> contiguous [B*HW, C, 1]: every spatial position becomes a row of a dense layer."""
+    B, C, HW = t.shape
+    return t.permute(0, 2, 1).reshape(B * HW, C, 1).contiguous()
+
+
+def _from_rows(t, B, HW):
+    """Inverse of _rows_view for a [B*HW, C, 1] tensor."""
+    return t.view(B, HW, t.size(1)).permute(0, 2, 1).contiguous()
+
+
+def _dense_route(x, weight, group):
+    """Conv-shaped calls (HW > 1) whose channel counts suit the tiled dense kernels are run as a
+    dense layer over B*HW rows (two permuting copies around the kernels).  Results are the same:
+    forward values, arg-max and bounds are per-row quantities, and the ordered weight gradient
+    adds its contributions in ascending b*HW + hw order either way."""
+    ci_g, co_g = weight.size(1), weight.size(0) // group
+    return x.size(2) > 1 and ci_g % 4 == 0 and co_g >= 32
+
+
 class DistF(torch.autograd.Function):
     """y[b,o,hw] = || x[b,g,:,hw] - weight[o,:] ||_p ; x [B,CI,HW], weight [CO,CI/group]."""
 
@@ -73,7 +93,12 @@ class DistF(torch.autograd.Function):
         if x.dim() != 3 or weight.dim() != 2:
             raise RuntimeError("input must be [B, CI, HW] and weight [CO, CI/group]")
         assert weight.size(1) * group == x.size(1)
-        B, CO, CI, G, HW = _shape5(x, weight, group)
+        if not (math.isinf(p) or p > 1):
+            raise NotImplementedError
+        ctx.rows = _dense_route(x, weight, group)
+        ctx.shape = (x.size(0), x.size(2))
+        xk = _rows_view(x) if ctx.rows else x
+        B, CO, CI, G, HW = _shape5(xk, weight, group)
         y = torch.empty(B, CO, HW, device=x.device, dtype=torch.float32)
         with torch.cuda.device(x.device):
             if math.isinf(p):
@@ -81,28 +106,26 @@ class DistF(torch.autograd.Function):
                 need = lib.linf_inf_dist_forward_workspace_bytes(B, CO, CI, G, HW)
                 if need:
                     ws = _workspace(x.device, need)
-                    rc = lib.linf_inf_dist_forward_ws(x.data_ptr(), weight.data_ptr(), B, CO, CI, G, HW,
+                    rc = lib.linf_inf_dist_forward_ws(xk.data_ptr(), weight.data_ptr(), B, CO, CI, G, HW,
                                                       y.data_ptr(), pos.data_ptr(), ws.data_ptr(),
                                                       ws.numel(), _stream())
                 else:
-                    rc = lib.linf_inf_dist_forward(x.data_ptr(), weight.data_ptr(), B, CO, CI, G, HW,
+                    rc = lib.linf_inf_dist_forward(xk.data_ptr(), weight.data_ptr(), B, CO, CI, G, HW,
                                                    y.data_ptr(), pos.data_ptr(), _stream())
                 _lib.check(rc, "inf_dist_forward")
-                ctx.save_for_backward(x, weight, y, pos)
-            elif p > 1:
-                rc = lib.linf_norm_dist_forward(x.data_ptr(), weight.data_ptr(), B, CO, CI, G, HW,
+                ctx.save_for_backward(xk, weight, y, pos)
+            else:
+                rc = lib.linf_norm_dist_forward(xk.data_ptr(), weight.data_ptr(), B, CO, CI, G, HW,
                                                 y.data_ptr(), float(p), _stream())
                 _lib.check(rc, "norm_dist_forward")
-                ctx.save_for_backward(x, weight, y)
-            else:
-                raise NotImplementedError
+                ctx.save_for_backward(xk, weight, y)
         ctx.group, ctx.p, ctx.tag = group, p, tag
-        return y
+        return _from_rows(y, *ctx.shape) if ctx.rows else y
 
     @staticmethod
     def backward(ctx, grad_output):
         lib = _lib.load()
-        grad_output = grad_output.contiguous()
+        grad_output = _rows_view(grad_output) if ctx.rows else grad_output.contiguous()
         _require(grad_output, "grad_output")
         need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         gx = gw = None
@@ -146,6 +169,8 @@ class DistF(torch.autograd.Function):
                         grad_output.data_ptr(), x.data_ptr(), weight.data_ptr(), y.data_ptr(),
                         B, CO, CI, G, HW, gw.data_ptr(), float(ctx.p), _stream())
                     _lib.check(rc, "norm_dist_backward_weight")
+        if ctx.rows and gx is not None:
+            gx = _from_rows(gx, *ctx.shape)
         return gx, gw, None, None, None
 
 
@@ -166,14 +191,20 @@ def inf_dist_bound(input_lower, input_upper, weight, group, use_custom_cuda_func
         _no_torch_branch()
     lib = _lib.load()
     _require(input_lower, "input_lower"); _require(input_upper, "input_upper"); _require(weight, "weight")
+    assert weight.size(1) * group == input_lower.size(1) and input_upper.shape == input_lower.shape
+    rows = _dense_route(input_lower, weight, group)
+    shape = (input_lower.size(0), input_lower.size(2))
+    if rows:
+        input_lower, input_upper = _rows_view(input_lower), _rows_view(input_upper)
     B, CO, CI, G, HW = _shape5(input_lower, weight, group)
-    assert weight.size(1) * group == CI and input_upper.shape == input_lower.shape
     lo = torch.empty(B, CO, HW, device=input_lower.device, dtype=torch.float32)
     up = torch.empty_like(lo)
     with torch.cuda.device(input_lower.device):
         rc = lib.linf_inf_dist_bound_forward(input_lower.data_ptr(), input_upper.data_ptr(), weight.data_ptr(),
                                              B, CO, CI, G, HW, lo.data_ptr(), up.data_ptr(), _stream())
     _lib.check(rc, "inf_dist_bound_forward")
+    if rows:
+        return _from_rows(lo, *shape), _from_rows(up, *shape)
     return lo, up
 
 

@@ -319,3 +319,50 @@ def test_pipelined_step_equals_plain_step(cuda, lib):
 
     for a, b in zip(run(False), run(True)):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("shape", [(4, 36, 64, 25, 1), (3, 32, 96, 9, 2), (2, 27, 40, 16, 1), (5, 64, 128, 4, 4)],
+                         ids=_ids)
+@pytest.mark.parametrize("p", [float("inf"), 8.0])
+def test_python_operator_conv_shapes(cuda, lib, shape, p):
+    """DistF / inf_dist_bound on conv-shaped inputs (HW > 1), incl. the shapes that are routed
+    through the dense kernels as B*HW rows: same results as the checker on the original layout."""
+    import linfdist_b200 as L
+    B, CI, CO, HW, G = shape
+    x, w, g = make_inputs(B, CI, CO, HW, G, seed=60 + CI, x_dist="uniform" if p == float("inf") else "normal")
+    xd = dev(x).requires_grad_(True); wd = dev(w).requires_grad_(True)
+    y = L.norm_dist(xd, wd, G, p)
+    y.backward(dev(g))
+    if p == float("inf"):
+        y_ref, pos_ref = oracle.inf_dist_forward(x, w, G)
+        gx_ref, gw_ref = oracle.inf_dist_backward(g, pos_ref, CI, G)
+        assert_bits_equal(y.detach(), y_ref, "values")
+        assert_bits_equal(xd.grad, gx_ref, "grad_input"); assert_bits_equal(wd.grad, gw_ref, "grad_weight")
+        lo = np.clip(x - 0.03, 0, 1).astype(np.float32); up = np.clip(x + 0.03, 0, 1).astype(np.float32)
+        yl, yu = L.inf_dist_bound(dev(lo), dev(up), dev(w), G)
+        yl_ref, yu_ref = oracle.inf_dist_bound(lo, up, w, G)
+        assert_bits_equal(yl, yl_ref, "lower"); assert_bits_equal(yu, yu_ref, "upper")
+    else:
+        y_ref = oracle.norm_dist_forward(x, w, G, p)
+        assert_lp_close(y.detach(), y_ref, "forward", floor=0.0)
+        gx_ref, gw_ref = oracle.norm_dist_backward(g, x, w, y_ref, G, p)
+        assert_lp_close(xd.grad, gx_ref, "grad_input"); assert_lp_close(wd.grad, gw_ref, "grad_weight")
+
+
+def test_norm_dist_conv_module(cuda, lib):
+    """NormDistConv (3x3, padding, stride) end to end against the checker on unfolded patches."""
+    import linfdist_b200 as L
+    import torch.nn.functional as F
+    torch.manual_seed(0)
+    m = L.NormDistConv(8, 32, 3, stride=2, padding=1, bias=True, mean_normalize=False).cuda()
+    L.set_p_norm(m, float("inf"))
+    x = torch.rand(3, 8, 9, 9, device="cuda")
+    y, _, _ = m(x)
+    cols = F.unfold(x, 3, 1, 1, 2)
+    y_ref, _ = oracle.inf_dist_forward(cols.cpu().numpy(), m.weight.detach().view(32, -1).cpu().numpy(), 1)
+    assert y.shape == (3, 32, 5, 5)
+    assert_bits_equal((y - m.bias.view(1, -1, 1, 1)).reshape(3, 32, 25), y_ref, "conv layer values")
+    m.eval()
+    lo = (x - 0.01).clamp(0, 1); up = (x + 0.01).clamp(0, 1)
+    y2, l2, u2 = m(x, lo, up)
+    assert (l2 <= y2 + 1e-6).all() and (y2 <= u2 + 1e-6).all()
