@@ -15,7 +15,8 @@ events around every step, an L2 flush between steps.  `e2e` repeats the measurem
 public Python API (norm_dist + autograd) with the step's inputs copied from pinned host memory
 and a scalar read back inside the timed region.  `roofline` relates the forward kernel to the
 FP32 non-FMA issue peak, `cpu_baseline` times the CPU checker (oracle/) on the host cores, and
-`train` reports the CIFAR-shape training step (5 distance layers, DDP over the same GPUs).
+`train` / `train_tiny` report the CIFAR-shape and TinyImageNet-shape training steps (BASELINE
+configs[3] and [4]; data parallel over the same GPUs).
 
 `--impl reference` times the CPU restatement of the reference path on the host cores only.
 """
@@ -260,17 +261,21 @@ def run_ours(args):
     e1.record()
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1) / e2e_steps)
-    clocks = sampler.stop() if sampler else None
 
     # ---- training step (CIFAR-shape net, DDP) ----------------------------------------------
-    train = None
+    train = train_tiny = None
     if not args.no_train:
         try:
             from linfdist_b200.train_step import bench_train_step
             train = bench_train_step(dev, world, rank, steps=args.train_steps, warmup=3)
         except Exception as exc:                                           # never lose the layer line
             train = {"error": repr(exc)}
+        try:
+            train_tiny = bench_train_step(dev, world, rank, steps=args.train_steps, warmup=3, config="tiny")
+        except Exception as exc:
+            train_tiny = {"error": repr(exc)}
 
+    clocks = sampler.stop() if sampler else None      # sampled across the layer, e2e and training legs
     if rank == 0:
         peaks = {}
         pk_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -306,6 +311,7 @@ def run_ours(args):
                                  "unit": "GB/s", "frac": bwd_bytes / (t_bwd * 1e-3) / 1e9 / hbm_peak},
             },
             "train": train,
+            "train_tiny": train_tiny,
         }
         if not args.no_cpu:
             rate, cores, sample = cpu_layer_rate()

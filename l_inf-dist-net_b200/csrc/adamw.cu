@@ -151,10 +151,10 @@ extern "C" int linf_adamw_step(float* param, const float* grad, float* exp_avg, 
             adamw_rows_kernel<0><<<rows, 256, 0, st>>>(a);
         }
     } else if (mode == 1) {
-        if (smem > 48 * 1024 && cudaFuncSetAttribute(adamw_rows_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return LINF_ERR_LAUNCH;
+        if (smem > 40 * 1024 && cudaFuncSetAttribute(adamw_rows_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return LINF_ERR_LAUNCH;
         adamw_rows_kernel<1><<<rows, 256, smem, st>>>(a);
     } else {
-        if (smem > 48 * 1024 && cudaFuncSetAttribute(adamw_rows_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return LINF_ERR_LAUNCH;
+        if (smem > 40 * 1024 && cudaFuncSetAttribute(adamw_rows_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return LINF_ERR_LAUNCH;
         adamw_rows_kernel<2><<<rows, 256, smem, st>>>(a);
     }
     return launch_status();

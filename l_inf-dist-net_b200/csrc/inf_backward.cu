@@ -594,7 +594,7 @@ template <int MODE, bool CTA_ROW, bool COMPACT, bool STAGED, bool APLACE>
 int launch_ordered_as(const float* g, const int* pos, const Dims& d, float* dst, cudaStream_t st,
                       int n_rows, int n_src, int warps, size_t smem) {
     auto kern = inf_backward_ordered_kernel<MODE, CTA_ROW, COMPACT, STAGED, APLACE>;
-    if (smem > 48 * 1024 &&
+    if (smem > 40 * 1024 &&
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT) != cudaSuccess)
         return LINF_ERR_LAUNCH;
     const int grid = CTA_ROW ? n_rows : (n_rows + warps - 1) / warps;
@@ -606,7 +606,7 @@ template <int MODE, bool CTA_ROW, int EPT>
 int launch_fast(const float* g, const int* pos, const Dims& d, float* dst, cudaStream_t st,
                 int n_rows, int n_src, int warps, size_t smem) {
     auto kern = inf_backward_rows_kernel<MODE, CTA_ROW, EPT>;
-    if (smem > 48 * 1024 &&
+    if (smem > 40 * 1024 &&
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT) != cudaSuccess)
         return LINF_ERR_LAUNCH;
     const int grid = CTA_ROW ? n_rows : (n_rows + warps - 1) / warps;

@@ -9,8 +9,8 @@ import torch
 import torch.nn as nn
 
 from .adamw import AdamW
-from .bound_module import BoundFinalIdentity
-from .nets import MLP, Model
+from .bound_module import BoundFinalIdentity, Predictor
+from .nets import MLP, MLPFeature, Model
 from .norm_dist import set_p_norm
 
 
@@ -38,6 +38,21 @@ def build_cifar_net(device, depth=5, width=5, p=float("inf"), eps=8.0 / 255.0, s
     net = Model(MLP(depth, width, (3, 32, 32), num_classes=10), BoundFinalIdentity(), eps).to(device)
     set_p_norm(net, p)
     return net
+
+
+def build_tiny_net(device, depth=5, width=5, hidden=512, p=float("inf"), eps=1.0 / 255.0, seed=2020):
+    """The '++' variant on TinyImageNet-shaped inputs (3x64x64 = 12288 features, 200 classes): `depth`
+    distance layers as feature extractor, then the reference's BoundLinear -> tanh -> BoundFinalLinear
+    head (model/bound_module.py:105-116; the reference head uses tanh, not ReLU)."""
+    torch.manual_seed(seed)
+    feat = MLPFeature(depth, width, (3, 64, 64))
+    net = Model(feat, Predictor(feat.out_features, hidden, 200), eps).to(device)
+    set_p_norm(net, p)
+    return net
+
+
+def cross_entropy():
+    return torch.nn.functional.cross_entropy
 
 
 class DataParallelStep:
@@ -149,17 +164,32 @@ class DataParallelStep:
             torch.cuda.current_stream().wait_stream(self.side)
 
 
-def bench_train_step(device, world, rank, steps=8, warmup=3, batch=512, p=float("inf")):
+def bench_train_step(device, world, rank, steps=8, warmup=3, batch=None, p=float("inf"), config="cifar"):
     """Times `steps` optimisation steps (after `warmup`), inputs copied from pinned host memory
-    every step.  Returns a dict with samples/s over all ranks (max step time over ranks)."""
+    every step.  Returns a dict with samples/s over all ranks (max step time over ranks).
+    config "cifar": 3x32x32 inputs, 5 distance layers 3072-5120x4-10, batch 512 per GPU, hinge loss;
+    config "tiny" : 3x64x64 inputs, 5 distance layers of width 5120 + tanh MLP head 5120-512-200,
+                    batch 256 per GPU, cross entropy on the worst-case margins."""
     import torch.distributed as dist
-    net = build_cifar_net(device, p=p)
-    opt = AdamW(net, lr=0.02, betas=(0.9, 0.99), eps=1e-10, weight_decay=5e-3)
+    if config == "cifar":
+        batch = batch or 512
+        net = build_cifar_net(device, p=p)
+        opt = AdamW(net, lr=0.02, betas=(0.9, 0.99), eps=1e-10, weight_decay=5e-3)
+        loss_fn = MarginLoss(hinge(0.75), kappa=1.0)
+        side, classes = 32, 10
+        what = "MLP 3072-5120x4-10, MeanNorm, eps 8/255, hinge(0.75), fused AdamW lr .02 wd 5e-3"
+    else:
+        batch = batch or 256
+        net = build_tiny_net(device, p=p)
+        opt = AdamW(net, lr=0.04, betas=(0.9, 0.99), eps=1e-10, weight_decay=5e-3)
+        loss_fn = MarginLoss(cross_entropy(), kappa=1.0)
+        side, classes = 64, 200
+        what = ("MLPFeature 12288-5120x5 + head 5120-512(tanh)-200, MeanNorm, eps 1/255, cross entropy, "
+                "fused AdamW lr .04 wd 5e-3")
     model = DataParallelStep(net, opt)
-    loss_fn = MarginLoss(hinge(0.75), kappa=1.0)
     gen = torch.Generator().manual_seed(4040 + rank)
-    images = torch.rand(batch, 3, 32, 32, generator=gen).pin_memory()
-    labels = torch.randint(0, 10, (batch,), generator=gen).pin_memory()
+    images = torch.rand(batch, 3, side, side, generator=gen).pin_memory()
+    labels = torch.randint(0, classes, (batch,), generator=gen).pin_memory()
     net.train()
 
     def step():
@@ -193,9 +223,10 @@ def bench_train_step(device, world, rank, steps=8, warmup=3, batch=512, p=float(
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     params = sum(q.numel() for q in net.parameters())
-    return {"metric": "CIFAR-shape L_inf-dist net train samples/s", "value": world * batch / (ms * 1e-3),
+    name = "CIFAR-shape L_inf-dist net" if config == "cifar" else "TinyImageNet-shape L_inf-dist net+MLP"
+    return {"metric": name + " train samples/s", "value": world * batch / (ms * 1e-3),
             "unit": "samples/s", "ms_per_step": ms, "steps": steps, "batch_per_gpu": batch, "n_gpus": world,
             "p": "inf" if math.isinf(p) else p, "loss": last, "parameters": params,
-            "config": "MLP 3072-5120x4-10, MeanNorm, eps 8/255, hinge(0.75), fused AdamW lr .02 wd 5e-3; "
+            "config": what + "; "
                       "n_gpus > 1: data parallel, one NCCL all-reduce (avg) per parameter issued as its gradient is "
                       "ready, optimiser applied per parameter as it arrives; backward mode as --backward"}
