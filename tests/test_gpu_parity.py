@@ -366,3 +366,59 @@ def test_norm_dist_conv_module(cuda, lib):
     lo = (x - 0.01).clamp(0, 1); up = (x + 0.01).clamp(0, 1)
     y2, l2, u2 = m(x, lo, up)
     assert (l2 <= y2 + 1e-6).all() and (y2 <= u2 + 1e-6).all()
+
+
+@pytest.mark.skipif(not os.path.exists(REF_LIB), reason="reference kernels were not prebuilt")
+def test_faster_than_reference_kernels(cuda, lib):
+    """Config-1 layer (B=512, Din=784, Dout=5120): forward + backward of this library against the
+    reference's own CUDA kernels compiled for sm_100a, same inputs, CUDA events, L2 flushed.  The
+    measured times are written to gpurun_out/ref_gpu_timing.json (when that folder can be made)."""
+    import json
+    from linfdist_b200 import _lib
+    from helpers import stream
+    ref = ctypes.CDLL(REF_LIB)
+    B, CI, CO = 512, 784, 5120
+    x, w, g = make_inputs(B, CI, CO, 1, 1, seed=2020)
+    xd, wd, gd = dev(x), dev(w), dev(g)
+    P = lambda t: ctypes.c_void_p(t.data_ptr())
+    y = torch.empty(B, CO, 1, device="cuda"); pos = torch.empty(B, CO, 1, device="cuda", dtype=torch.int32)
+    gx = torch.empty_like(xd); gw = torch.empty_like(wd)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    L = _lib.load()
+
+    def ours():
+        rc = L.linf_inf_dist_forward(xd.data_ptr(), wd.data_ptr(), B, CO, CI, 1, 1, y.data_ptr(), pos.data_ptr(), stream())
+        rc |= L.linf_inf_dist_backward_input(gd.data_ptr(), pos.data_ptr(), B, CO, CI, 1, 1, gx.data_ptr(), stream())
+        rc |= L.linf_inf_dist_backward_weight(gd.data_ptr(), pos.data_ptr(), B, CO, CI, 1, 1, gw.data_ptr(), stream())
+        assert rc == 0
+
+    def theirs():
+        ref.ref_inf_dist_forward(P(xd), P(wd), B, CO, CI, 1, 1, P(y), P(pos))
+        gx.zero_(); gw.zero_()
+        ref.ref_inf_dist_backward_input(P(gd), P(pos), B, CO, CI, 1, 1, P(gx))
+        ref.ref_inf_dist_backward_weight(P(gd), P(pos), B, CO, CI, 1, 1, P(gw))
+
+    def time_ms(fn, n=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(n):
+            flush.zero_()
+            e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record(); torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return sorted(ts)[len(ts) // 2]
+
+    t_ours, t_ref = time_ms(ours), time_ms(theirs)
+    terms = B * CI * CO
+    report = {"workload": "inf-dist layer fwd+bwd, B=512, Din=784, Dout=5120", "ours_ms": t_ours, "reference_kernels_ms": t_ref,
+              "ours_terms_per_s": terms / (t_ours * 1e-3), "reference_terms_per_s": terms / (t_ref * 1e-3),
+              "speedup": t_ref / t_ours}
+    try:
+        os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
+        json.dump(report, open(os.path.join(ROOT, "gpurun_out", "ref_gpu_timing.json"), "w"), indent=1)
+    except OSError:
+        pass
+    print(report)
+    assert t_ours < t_ref, report
