@@ -197,10 +197,8 @@ def run_ours(args):
 
     def bwd():
         if args.backward == "ordered":
-            _lib.check(lib.linf_inf_dist_backward_input(g.data_ptr(), pos.data_ptr(), B, DOUT, DIN, 1, 1,
-                                                        gx.data_ptr(), stream), "backward_input")
-            _lib.check(lib.linf_inf_dist_backward_weight(g.data_ptr(), pos.data_ptr(), B, DOUT, DIN, 1, 1,
-                                                         gw.data_ptr(), stream), "backward_weight")
+            _lib.check(lib.linf_inf_dist_backward(g.data_ptr(), pos.data_ptr(), B, DOUT, DIN, 1, 1,
+                                                  gx.data_ptr(), gw.data_ptr(), stream), "backward")
         else:
             gx.zero_(); gw.zero_()
             _lib.check(lib.linf_inf_dist_backward_atomic(g.data_ptr(), pos.data_ptr(), B, DOUT, DIN, 1, 1,

@@ -138,6 +138,17 @@ int linf_inf_dist_backward_weight(const float* grad_output, const int* pos,
                                   float* grad_weight, void* stream);
 
 /*
+ * Both ordered gradients in one call: the same results, bit for bit, as
+ * linf_inf_dist_backward_input followed by linf_inf_dist_backward_weight, but the two kernels run
+ * side by side (grad_weight on a library-owned helper stream that forks from and joins back into
+ * `stream`, so to the caller the call is ordered on `stream` like any other).  Replaces the pair of
+ * launches at model/norm_dist.py:34-38.
+ */
+int linf_inf_dist_backward(const float* grad_output, const int* pos,
+                           int B, int CO, int CI, int G, int HW,
+                           float* grad_input, float* grad_weight, void* stream);
+
+/*
  * Both gradients in one pass over (grad_output, pos) with warp-aggregated fp32 atomics:
  * contributions of one warp that hit the same address are summed in lane order first and
  * issued as one atomic.  The buffers are ACCUMULATED into, exactly like the reference

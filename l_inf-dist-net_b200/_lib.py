@@ -25,6 +25,7 @@ _PROTOS = {
     "linf_inf_dist_bound_forward": [_F, _F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F, _F],
     "linf_inf_dist_backward_input": [_F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F],
     "linf_inf_dist_backward_weight": [_F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F],
+    "linf_inf_dist_backward": [_F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F, _F],
     "linf_inf_dist_backward_atomic": [_F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F, _F],
     "linf_adamw_step": [_F, _F, _F, _F, _INT, _INT, ctypes.c_float, ctypes.c_float, ctypes.c_float, ctypes.c_float,
                         ctypes.c_float, ctypes.c_float, _INT, _F],

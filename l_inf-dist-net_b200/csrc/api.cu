@@ -111,6 +111,15 @@ int linf_inf_dist_backward_weight(const float* grad_output, const int* pos, int 
     return inf_backward_weight(grad_output, pos, d, grad_weight, as_stream(stream));
 }
 
+int linf_inf_dist_backward(const float* grad_output, const int* pos, int B, int CO, int CI, int G, int HW,
+                           float* grad_input, float* grad_weight, void* stream) {
+    if (!grad_output || !pos || !grad_input || !grad_weight) return LINF_ERR_NULL;
+    Dims d;
+    int rc = make_dims(B, CO, CI, G, HW, &d);
+    if (rc) return rc;
+    return inf_backward_ordered_both(grad_output, pos, d, grad_input, grad_weight, as_stream(stream));
+}
+
 int linf_inf_dist_backward_atomic(const float* grad_output, const int* pos, int B, int CO, int CI, int G, int HW,
                                   float* grad_input, float* grad_weight, void* stream) {
     if (!grad_output || !pos) return LINF_ERR_NULL;

@@ -84,6 +84,8 @@ int inf_backward_input(const float* g, const int* pos, const Dims& d, float* gx,
 int inf_backward_weight(const float* g, const int* pos, const Dims& d, float* gw, cudaStream_t st);
 int inf_backward_atomic(const float* g, const int* pos, const Dims& d, float* gx, float* gw,
                         cudaStream_t st);
+int inf_backward_ordered_both(const float* g, const int* pos, const Dims& d, float* gx, float* gw,
+                              cudaStream_t st);
 // few output channels per group (skinny.cu)
 bool skinny_ok(const Dims& d, const void* a, const void* b, const void* c);
 int inf_forward_skinny(const float* x, const float* w, const Dims& d, float* y, int* pos, cudaStream_t st);

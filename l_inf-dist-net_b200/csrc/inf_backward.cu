@@ -22,6 +22,8 @@
 // for grad_weight a 32 x 32 tile is transposed through shared memory so that the lanes of a
 // warp run over the batch for one output channel, equal bins are combined inside the warp and
 // one atomic is issued per distinct bin.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace linf {
@@ -362,7 +364,7 @@ inf_backward_rows_kernel(const float* __restrict__ gout, const int* __restrict__
             const int g = rowj / d.COg, o = rowj - g * d.COg, b = e / HW, hw = e - b * HW;
             return ((size_t)(b * d.G + g) * d.COg + o) * HW + hw;
         };
-        constexpr int SU = 4;                            // loads in flight per thread
+        constexpr int SU = 8;                            // loads in flight per thread
         for (int q0 = threadIdx.x; q0 < total; q0 += SU * blockDim.x) {
             int pj[SU], pe[SU], pp[SU]; float pg[SU];
 #pragma unroll
@@ -523,6 +525,15 @@ inf_backward_rows_kernel(const float* __restrict__ gout, const int* __restrict__
             const int s0 = seg[i], s1 = seg[i + 1];
             float acc = 0.f;
             int j = s0;
+            // long bins (one bin often collects most of a weight row's sources): keep 16 loads in
+            // flight ahead of the dependent chain of adds
+            for (; j + 16 <= s1; j += 16) {
+                float v[16];
+#pragma unroll
+                for (int q = 0; q < 16; ++q) v[q] = sorted[j + q];
+#pragma unroll
+                for (int q = 0; q < 16; ++q) acc += v[q];
+            }
             for (; j + 4 <= s1; j += 4) {
                 const float v0 = sorted[j], v1 = sorted[j + 1], v2 = sorted[j + 2], v3 = sorted[j + 3];
                 acc += v0; acc += v1; acc += v2; acc += v3;
@@ -628,6 +639,7 @@ int launch_ordered(const float* g, const int* pos, const Dims& d, float* dst, cu
             if (rpc > 8) rpc = 8;
             if (rpc >= 1) {
                 // keep at least two CTAs per SM when eight rows would take more than half of it
+                while (rpc & (rpc - 1)) --rpc;                       // power of two
                 while (rpc > 2 && gb * rpc > 100 * 1024) rpc >>= 1;
                 if (n_src <= 128) rc = launch_fast<MODE, false, 4>(g, pos, d, dst, st, n_rows, n_src, rpc, gb * rpc);
                 else if (n_src <= 256) rc = launch_fast<MODE, false, 8>(g, pos, d, dst, st, n_rows, n_src, rpc, gb * rpc);
@@ -681,6 +693,37 @@ int inf_backward_input(const float* g, const int* pos, const Dims& d, float* gx,
 
 int inf_backward_weight(const float* g, const int* pos, const Dims& d, float* gw, cudaStream_t st) {
     return launch_ordered<1>(g, pos, d, gw, st);
+}
+
+// Both ordered gradients.  The two kernels are independent and each of them is bound by the
+// latency of its sort phases rather than by throughput, so they are run side by side: grad_weight
+// on a helper stream that forks from, and joins back into, the caller's stream.  The helper stream
+// and its two events are created once per device and never destroyed.
+int inf_backward_ordered_both(const float* g, const int* pos, const Dims& d, float* gx, float* gw,
+                              cudaStream_t st) {
+    struct Side { cudaStream_t stream; cudaEvent_t fork, join; bool ok; };
+    static Side sides[16] = {};
+    static std::mutex lock;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return LINF_ERR_LAUNCH;
+    Side* s = &sides[dev];
+    {
+        std::lock_guard<std::mutex> hold(lock);
+        if (!s->ok) {
+            if (cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking) != cudaSuccess ||
+                cudaEventCreateWithFlags(&s->fork, cudaEventDisableTiming) != cudaSuccess ||
+                cudaEventCreateWithFlags(&s->join, cudaEventDisableTiming) != cudaSuccess)
+                return LINF_ERR_LAUNCH;
+            s->ok = true;
+        }
+    }
+    if (cudaEventRecord(s->fork, st) != cudaSuccess || cudaStreamWaitEvent(s->stream, s->fork, 0) != cudaSuccess)
+        return LINF_ERR_LAUNCH;
+    int rc = launch_ordered<1>(g, pos, d, gw, s->stream);
+    const int rc2 = launch_ordered<0>(g, pos, d, gx, st);
+    if (cudaEventRecord(s->join, s->stream) != cudaSuccess || cudaStreamWaitEvent(st, s->join, 0) != cudaSuccess)
+        return LINF_ERR_LAUNCH;
+    return rc ? rc : rc2;
 }
 
 int inf_backward_atomic(const float* g, const int* pos, const Dims& d, float* gx, float* gw,

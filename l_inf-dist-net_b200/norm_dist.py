@@ -143,6 +143,11 @@ class DistF(torch.autograd.Function):
                             grad_output.data_ptr(), pos.data_ptr(), B, CO, CI, G, HW,
                             gx.data_ptr() if need_x else None, gw.data_ptr() if need_w else None, _stream())
                         _lib.check(rc, "inf_dist_backward_atomic")
+                elif need_x and need_w:
+                    gx = torch.empty_like(x); gw = torch.empty_like(weight)
+                    rc = lib.linf_inf_dist_backward(grad_output.data_ptr(), pos.data_ptr(), B, CO, CI, G, HW,
+                                                    gx.data_ptr(), gw.data_ptr(), _stream())
+                    _lib.check(rc, "inf_dist_backward")
                 else:
                     if need_x:
                         gx = torch.empty_like(x)

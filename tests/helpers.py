@@ -65,6 +65,11 @@ def c_inf_backward(g, pos, CI, G, mode="ordered"):
         assert rc == 0, lib.linf_error_string(rc)
         rc = lib.linf_inf_dist_backward_weight(g.data_ptr(), pos.data_ptr(), B, CO, CI, G, HW, gw.data_ptr(), stream())
         assert rc == 0, lib.linf_error_string(rc)
+    elif mode == "both":
+        gx = torch.full((B, CI, HW), float("nan"), device=g.device)
+        gw = torch.full((CO, CI // G), float("nan"), device=g.device)
+        rc = lib.linf_inf_dist_backward(g.data_ptr(), pos.data_ptr(), B, CO, CI, G, HW, gx.data_ptr(), gw.data_ptr(), stream())
+        assert rc == 0, lib.linf_error_string(rc)
     else:
         gx = torch.zeros(B, CI, HW, device=g.device); gw = torch.zeros(CO, CI // G, device=g.device)
         rc = lib.linf_inf_dist_backward_atomic(g.data_ptr(), pos.data_ptr(), B, CO, CI, G, HW,

@@ -98,6 +98,8 @@ def test_inf_backward(cuda, lib, shape):
     gx_ref, gw_ref = oracle.inf_dist_backward(g, pos, CI, G)
     gx, gw = c_inf_backward(dev(g), dev(pos), CI, G, "ordered")
     assert_bits_equal(gx, gx_ref, "ordered grad_input"); assert_bits_equal(gw, gw_ref, "ordered grad_weight")
+    gxb, gwb = c_inf_backward(dev(g), dev(pos), CI, G, "both")
+    assert_bits_equal(gxb, gx_ref, "side-by-side grad_input"); assert_bits_equal(gwb, gw_ref, "side-by-side grad_weight")
     gxa, gwa = c_inf_backward(dev(g), dev(pos), CI, G, "atomic")
     np.testing.assert_allclose(gxa.cpu().numpy(), gx_ref, rtol=1e-4, atol=1e-4)
     np.testing.assert_allclose(gwa.cpu().numpy(), gw_ref, rtol=1e-4, atol=1e-4)
