@@ -89,7 +89,7 @@ int linf_inf_dist_forward_ws(const float* input, const float* weight,
  *     holds (the need grows with the SM count of the GPU and, slowly, with the number of output
  *     tiles; on a 148-SM B200 every layer the library accepts fits).
  *   - The first call on each device looks up the device address of the array (with that device
- *     current).  Make that first call once during set-up, before any stream capture begins.
+ *     current); later calls on that device reuse it.
  *   - All calls on one GPU share the one array, and it keeps whatever the last call left there;
  *     the call clears the part that has to start at zero.  Two calls that overlap on the same
  *     GPU (different streams or threads) race on it: run them one after the other.

@@ -424,3 +424,42 @@ def test_faster_than_reference_kernels(cuda, lib):
         pass
     print(report)
     assert t_ours < t_ref, report
+
+
+def test_workspace_errors_and_determinism(cuda, lib):
+    """A workspace that is too small or misaligned is refused with a code (no launch); a split-k
+    forward gives the same bits on every run although the last-arriving CTA differs."""
+    from helpers import stream
+    B, CI, CO = 512, 3072, 5120
+    need = lib.linf_inf_dist_forward_workspace_bytes(B, CO, CI, 1, 1)
+    assert need > 0
+    x = torch.rand(B, CI, 1, device="cuda"); w = torch.randn(CO, CI, device="cuda")
+    y = torch.empty(B, CO, 1, device="cuda"); pos = torch.empty(B, CO, 1, device="cuda", dtype=torch.int32)
+    ws = torch.empty(need + 512, dtype=torch.uint8, device="cuda")
+    args = (x.data_ptr(), w.data_ptr(), B, CO, CI, 1, 1, y.data_ptr(), pos.data_ptr())
+    assert lib.linf_inf_dist_forward_ws(*args, ws.data_ptr(), need - 1, stream()) == 6          # too small
+    assert lib.linf_inf_dist_forward_ws(*args, ws.data_ptr() + 4, need, stream()) == 6          # misaligned
+    assert lib.linf_inf_dist_forward_ws(*args, None, 0, stream()) == 6                          # missing
+    runs = []
+    for _ in range(3):
+        assert lib.linf_inf_dist_forward_ws(*args, ws.data_ptr(), need, stream()) == 0
+        torch.cuda.synchronize()
+        runs.append((y.clone(), pos.clone()))
+    for yy, pp in runs[1:]:
+        assert torch.equal(yy, runs[0][0]) and torch.equal(pp, runs[0][1])
+    y0, p0 = c_inf_forward(x, w, 1, use_ws=False)
+    assert torch.equal(y0, runs[0][0]) and torch.equal(p0, runs[0][1])
+
+
+def test_lp_shapes_that_leave_the_tiled_path(cuda, lib):
+    """Channel counts that are not multiples of 4, and p beyond the tiled instantiations, take the
+    generic kernels: same tolerance."""
+    for (B, CI, CO, p) in [(9, 66, 34, 8.0), (5, 64, 33, 16.0), (70, 128, 96, 1500.5), (33, 100, 64, 2.5)]:
+        x, w, g = make_inputs(B, CI, CO, 1, 1, seed=31 + CO, x_dist="normal")
+        y_ref = oracle.norm_dist_forward(x, w, 1, p)
+        y = c_lp_forward(dev(x), dev(w), 1, p)
+        assert_lp_close(y, y_ref, f"forward {B,CI,CO,p}", floor=0.0)
+        gx_ref, gw_ref = oracle.norm_dist_backward(g, x, w, y_ref, 1, p)
+        gx, gw = c_lp_backward(dev(g), dev(x), dev(w), dev(y_ref), 1, p)
+        rtol = 1e-5 if p <= 64 else 1e-5 * p / 64
+        assert_lp_close(gx, gx_ref, f"grad_input {p}", rtol=rtol); assert_lp_close(gw, gw_ref, f"grad_weight {p}", rtol=rtol)
