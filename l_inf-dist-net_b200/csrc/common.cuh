@@ -84,6 +84,8 @@ int inf_backward_input(const float* g, const int* pos, const Dims& d, float* gx,
 int inf_backward_weight(const float* g, const int* pos, const Dims& d, float* gw, cudaStream_t st);
 int inf_backward_atomic(const float* g, const int* pos, const Dims& d, float* gx, float* gw,
                         cudaStream_t st);
+// sort-free ordered grad_weight for dense layers (inf_backward_accum.cu); -1 = shape not taken
+int inf_backward_weight_accum(const float* g, const int* pos, const Dims& d, float* gw, cudaStream_t st);
 int inf_backward_ordered_both(const float* g, const int* pos, const Dims& d, float* gx, float* gw,
                               cudaStream_t st);
 // few output channels per group (skinny.cu)

@@ -630,6 +630,11 @@ int launch_ordered(const float* g, const int* pos, const Dims& d, float* dst, cu
     const int n_rows = (MODE == 0) ? d.R * d.G : d.CO;
     const int n_src = (MODE == 0) ? d.COg : d.R;
     const int nb = d.CIg;
+    if (MODE == 1) {
+        // dense layers: the sort-free kernel
+        int rc = inf_backward_weight_accum(g, pos, d, dst, st);
+        if (rc >= 0) return rc;
+    }
     {
         // fast path (sources held in registers) whenever the row fits its thread group
         int rc = -1;

@@ -1,0 +1,180 @@
+// Ordered grad_weight of the inf-dist backward for dense layers (HW == 1) without a sort.
+//
+// One warp owns an output-channel row of grad_weight, keeps the whole row (CIg floats, all +0 at
+// the start) in shared memory, and walks the row's sources -- the batch rows r = 0..R-1 -- 32 at
+// a time in ascending order.  Lanes of one batch that hit the same bin are found with match_any;
+// the lowest of them adds the bin's old value and then the lanes' values, one by one in lane
+// order, and writes the bin back.  Every bin therefore sees exactly the sequential fp32 adds
+// from +0 in ascending source order that the sort-based kernels (inf_backward.cu) produce, but
+// the histogram, the scan over all bins and the per-bin loops of the sort are gone: what is left
+// per row is 16 batches (R = 512) plus zeroing and copying the row.  The finished row is written
+// out whole, so the destination needs no zero fill.
+//
+// The sources of a row lie CO floats apart.  The CTA therefore first copies a block of sources
+// of its (up to 8) neighbouring rows into shared memory, 8 consecutive threads reading 8
+// consecutive channels, so that every 32-byte sector of grad_output / pos is fetched once.
+//
+// grad_input keeps the sort: its rows are few (R) and long (COg sources), one warp per row is
+// latency bound (measured 64 us at R = 512, COg = 5120, against 28 us for the sort), and sharing
+// a row between warps by bin ownership multiplies the scan of the sources by the warp count.
+#include "common.cuh"
+
+namespace linf {
+namespace {
+
+constexpr unsigned FULL = 0xffffffffu;
+constexpr int SB = 512;          // sources per staged block
+
+// One batch of up to 32 sources, one per lane: bin `idx` (idx >= nb = no source / dropped) and
+// signed value `v`.
+struct Batch {
+    int idx; float v;
+    unsigned grp;       // lanes with the same bin as this one (0 = no source here)
+    unsigned dup;       // lanes that are not the lowest of their bin (same for the whole warp)
+};
+
+// match_any costs one pass per DISTINCT value among the lanes; rows of grad_weight have few (one
+// bin usually takes most of a row's sources).  One vote per bit of the bin index -- a cost
+// independent of the data -- measured slower on such rows (43 us against 35 us at B = 512,
+// Din = 784, Dout = 5120).
+__device__ __forceinline__ Batch classify(int idx, float v, int nb, int lane) {
+    Batch b;
+    b.idx = idx; b.v = v; b.grp = 0;
+    const bool active = idx < nb;
+    const unsigned act = __ballot_sync(FULL, active);
+    if (active) b.grp = __match_any_sync(act, idx);
+    b.dup = __ballot_sync(FULL, (b.grp & ((1u << lane) - 1u)) != 0);
+    return b;
+}
+
+// `staged_v`: the 32 signed values of this batch in shared memory (16-byte aligned).
+__device__ __forceinline__ void add_batch(float* __restrict__ acc, const Batch& b, int lane,
+                                          const float* __restrict__ staged_v) {
+    const bool active = b.grp != 0;
+    const bool leader = active && (b.grp & ((1u << lane) - 1u)) == 0;
+    float a = active ? acc[b.idx] + b.v : 0.f;       // only the leader's sum is kept
+    if (b.dup != 0) {
+        if (__popc(b.dup) > 8) {
+            // many lanes share bins: every leader reads the batch's 32 signed values from shared
+            // memory, 4 at a time, and adds those of its own group -- a fixed cost, where one
+            // shuffle per duplicate lane would not be
+            const unsigned rest = b.grp & ~(1u << lane);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const float4 w4 = *reinterpret_cast<const float4*>(staged_v + 4 * q);
+                if ((rest >> (4 * q + 0)) & 1u) a += w4.x;
+                if ((rest >> (4 * q + 1)) & 1u) a += w4.y;
+                if ((rest >> (4 * q + 2)) & 1u) a += w4.z;
+                if ((rest >> (4 * q + 3)) & 1u) a += w4.w;
+            }
+        } else {
+            unsigned todo = b.dup;
+            while (todo) {
+                const int l = __ffs(todo) - 1;
+                todo &= todo - 1;
+                const float vl = __shfl_sync(FULL, b.v, l);
+                if ((b.grp >> l) & 1u) a += vl;
+            }
+        }
+    }
+    if (leader) acc[b.idx] = a;
+    __syncwarp();
+}
+
+__global__ void __launch_bounds__(256)
+inf_backward_weight_accum_kernel(const float* __restrict__ gout, const int* __restrict__ pos, Dims d,
+                                 float* __restrict__ dst, int nbp, int vec_out) {
+    extern __shared__ __align__(16) float smem_f[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int rpc = blockDim.x >> 5;
+    const int n_rows = d.CO, n_src = d.R, nb = d.CIg;
+    const int row0 = blockIdx.x * rpc, row = row0 + warp;    // row = g * COg + o
+    float* acc = smem_f + (size_t)warp * nbp;
+    for (int i = lane * 4; i < nbp; i += 128) *reinterpret_cast<float4*>(acc + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+    __syncwarp();
+
+    // staging area behind the rows: [rpc][SB] pos words, [rpc][SB] signed values
+    int* spos = reinterpret_cast<int*>(smem_f + (size_t)rpc * nbp);
+    float* sval = reinterpret_cast<float*>(spos + (size_t)rpc * SB);
+    for (int s0 = 0; s0 < n_src; s0 += SB) {
+        const int cnt = min(SB, n_src - s0);
+        const int total = cnt * rpc;
+        constexpr int SU = 8;                             // loads in flight per thread
+        for (int q0 = threadIdx.x; q0 < total; q0 += SU * blockDim.x) {
+            int pp[SU]; float pg[SU];
+#pragma unroll
+            for (int u = 0; u < SU; ++u) {
+                const int q = q0 + u * blockDim.x;
+                pp[u] = -1; pg[u] = 0.f;
+                if (q < total) {
+                    const int j = q % rpc, e = q / rpc;
+                    // source r of row (g, o): element (r * G + g) * COg + o = r * CO + row
+                    const size_t a = (size_t)(s0 + e) * d.CO + min(row0 + j, n_rows - 1);
+                    pp[u] = __ldg(pos + a); pg[u] = __ldg(gout + a);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < SU; ++u) {
+                const int q = q0 + u * blockDim.x;
+                if (q < total) {
+                    const int j = q % rpc, e = q / rpc;
+                    spos[j * SB + e] = pp[u];
+                    sval[j * SB + e] = (pp[u] >= 0) ? -pg[u] : pg[u];     // grad_weight takes -s * g
+                }
+            }
+        }
+        __syncthreads();
+        if (row < n_rows) {
+            const int* mp = spos + warp * SB;
+            const float* mv = sval + warp * SB;
+            // groups of 4 batches: the grouping of all four is issued before the first is added
+            for (int b0 = 0; b0 * 32 < cnt; b0 += 4) {
+                Batch bt[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int e = (b0 + u) * 32 + lane;
+                    bt[u] = classify(e < cnt ? (mp[e] & 0x7fffffff) : 0x7fffffff, e < cnt ? mv[e] : 0.f, nb, lane);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if ((b0 + u) * 32 < cnt) add_batch(acc, bt[u], lane, mv + (b0 + u) * 32);
+            }
+        }
+        __syncthreads();
+    }
+    if (row >= n_rows) return;
+    float* out = dst + (size_t)row * nb;
+    if (vec_out) {
+        for (int i = lane * 4; i < nb; i += 128)
+            *reinterpret_cast<float4*>(out + i) = *reinterpret_cast<const float4*>(acc + i);
+    } else {
+        for (int i = lane; i < nb; i += 32) out[i] = acc[i];
+    }
+}
+
+}  // namespace
+
+// Returns -1 when the shape is not one this kernel takes (the caller falls back to the sort).
+int inf_backward_weight_accum(const float* g, const int* pos, const Dims& d, float* gw, cudaStream_t st) {
+    if (d.HW != 1) return -1;
+    const int nbp = (d.CIg + 3) & ~3;
+    const size_t limit = 200 * 1024;
+    const size_t per_row = (size_t)nbp * 4 + (size_t)SB * 8;
+    if (per_row > limit) return -1;
+    // Rows per CTA.  Neighbouring rows share the sectors of the strided sources: 8 rows use every
+    // sector whole, but two CTAs per SM (one staging while the other adds) are worth more.
+    int rpc = 8;
+    while (rpc > 1 && (size_t)rpc * per_row > limit) rpc >>= 1;
+    while (rpc > 2 && (size_t)rpc * per_row > 100 * 1024) rpc >>= 1;
+    const size_t smem = (size_t)rpc * per_row;
+    if (smem > 40 * 1024 &&
+        cudaFuncSetAttribute(inf_backward_weight_accum_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)limit) != cudaSuccess)
+        return LINF_ERR_LAUNCH;
+    const int vec_out = ((d.CIg & 3) == 0 && (reinterpret_cast<uintptr_t>(gw) & 15u) == 0) ? 1 : 0;
+    const int grid = (d.CO + rpc - 1) / rpc;
+    inf_backward_weight_accum_kernel<<<grid, 32 * rpc, smem, st>>>(g, pos, d, gw, nbp, vec_out);
+    return launch_status();
+}
+
+}  // namespace linf

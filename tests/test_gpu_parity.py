@@ -463,3 +463,32 @@ def test_lp_shapes_that_leave_the_tiled_path(cuda, lib):
         gx, gw = c_lp_backward(dev(g), dev(x), dev(w), dev(y_ref), 1, p)
         rtol = 1e-5 if p <= 64 else 1e-5 * p / 64
         assert_lp_close(gx, gx_ref, f"grad_input {p}", rtol=rtol); assert_lp_close(gw, gw_ref, f"grad_weight {p}", rtol=rtol)
+
+
+@pytest.mark.parametrize("pattern", ["one_bin", "two_bins", "uniform", "out_of_range", "runs"])
+@pytest.mark.parametrize("shape", [(1100, 785, 96, 1), (40, 784, 1300, 1), (64, 60, 2048, 2), (513, 36, 520, 1)],
+                         ids=lambda s: "B{}_CI{}_CO{}_G{}".format(*s))
+def test_inf_backward_synthetic_positions(cuda, lib, pattern, shape):
+    """The ordered scatter on position patterns a forward pass rarely produces: every source of a
+    row in one bin, two alternating bins, indices outside the group (dropped), long runs; row
+    lengths that are not multiples of 32, of the staging block or of 4."""
+    B, CI, CO, G = shape
+    CIg = CI // G
+    rng = np.random.default_rng(len(pattern) * 100 + B)
+    if pattern == "one_bin":
+        idx = np.full((B, CO, 1), CIg - 1, dtype=np.int64)
+    elif pattern == "two_bins":
+        idx = (np.arange(B)[:, None, None] + np.arange(CO)[None, :, None]) % 2 * (CIg - 1)
+    elif pattern == "uniform":
+        idx = rng.integers(0, CIg, (B, CO, 1))
+    elif pattern == "out_of_range":
+        idx = rng.integers(0, CIg + 40, (B, CO, 1))
+    else:
+        idx = (np.arange(B)[:, None, None] // 37 + np.arange(CO)[None, :, None] // 45) % CIg
+    sign = rng.integers(0, 2, (B, CO, 1)).astype(np.uint32) << 31
+    pos = (idx.astype(np.uint32) | sign).view(np.int32)
+    g = rng.standard_normal((B, CO, 1)).astype(np.float32)
+    gx_ref, gw_ref = oracle.inf_dist_backward(g, pos, CI, G)
+    for mode in ("ordered", "both"):
+        gx, gw = c_inf_backward(dev(g), dev(pos), CI, G, mode)
+        assert_bits_equal(gx, gx_ref, f"{mode} grad_input"); assert_bits_equal(gw, gw_ref, f"{mode} grad_weight")
