@@ -118,31 +118,48 @@ __device__ __forceinline__ long long unit_begin(const TiledParams& p, int c) {
     return total * c / p.n_cta;
 }
 
+// cp.async sources of one thread for the k-tiles of an output tile.  A thread always copies the
+// same 16-byte column `ch` of the same rows (32 rows apart) of x and of w; only k advances from
+// tile to tile.  The row part of the address is worked out once per output tile and kept as a
+// 32-bit element offset (tensors of the tiled path have fewer than 2^31 elements), so that a
+// k-tile costs one add and one copy instruction per 16 bytes.
 template <class GEO>
-__device__ __forceinline__ void load_stage(float* stage, const TiledParams& p, int g, int m0, int n0,
-                                           int kt, int tid) {
-    constexpr int CH = GEO::BK / 4;  // 16-byte chunks per row
+struct StageSrc {
+    static constexpr int CH = GEO::BK / 4;             // 16-byte chunks per row
+    static constexpr int RPP = GEO::NT / CH;           // rows per pass of the CTA
+    static constexpr int PA = GEO::BM / RPP, PB = GEO::BN / RPP;
+    unsigned a[PA], b[PB];                             // element offsets of (row, 4 * ch) in x and w
+    int kin;                                           // 4 * ch: first k this thread copies in a tile
+    int dst;                                           // float offset of (row0, ch) in a stage's A block
+};
+
+template <class GEO>
+__device__ __forceinline__ StageSrc<GEO> stage_src(const TiledParams& p, int g, int m0, int n0, int tid) {
+    StageSrc<GEO> s;
+    const int row = tid / s.CH, ch = tid % s.CH;
+    s.kin = 4 * ch;
+    s.dst = row * GEO::LD + 4 * ch;
+#pragma unroll
+    for (int u = 0; u < s.PA; ++u)
+        s.a[u] = (unsigned)min(m0 + row + u * s.RPP, p.M - 1) * (unsigned)p.lda + (unsigned)g * (unsigned)p.K + 4u * ch;
+#pragma unroll
+    for (int u = 0; u < s.PB; ++u)
+        s.b[u] = ((unsigned)g * (unsigned)p.N + (unsigned)min(n0 + row + u * s.RPP, p.N - 1)) * (unsigned)p.K + 4u * ch;
+    return s;
+}
+
+template <class GEO>
+__device__ __forceinline__ void load_stage(float* stage, const TiledParams& p, const StageSrc<GEO>& s, int kt) {
     const int k0 = kt * GEO::BK;
-    float* As = stage;
-    float* Bs = stage + GEO::BM * GEO::LD;
+    const bool in = k0 + s.kin < p.K;                  // past the end of the row: zero fill
+    const unsigned kk = in ? (unsigned)k0 : 0u;
+    const int bytes = in ? 16 : 0;
+    float* As = stage + s.dst;
+    float* Bs = As + GEO::BM * GEO::LD;
 #pragma unroll
-    for (int q = tid; q < GEO::BM * CH; q += GEO::NT) {
-        int row = q / CH, ch = q % CH;
-        int m = min(m0 + row, p.M - 1);
-        int k = k0 + ch * 4;
-        bool in = k < p.K;
-        const float* src = p.x + (size_t)m * p.lda + (size_t)g * p.K + (in ? k : 0);
-        cp_async16(As + row * GEO::LD + ch * 4, src, in ? 16 : 0);
-    }
+    for (int u = 0; u < s.PA; ++u) cp_async16(As + u * s.RPP * GEO::LD, p.x + (size_t)(s.a[u] + kk), bytes);
 #pragma unroll
-    for (int q = tid; q < GEO::BN * CH; q += GEO::NT) {
-        int row = q / CH, ch = q % CH;
-        int n = min(n0 + row, p.N - 1);
-        int k = k0 + ch * 4;
-        bool in = k < p.K;
-        const float* src = p.w + ((size_t)g * p.N + n) * p.K + (in ? k : 0);
-        cp_async16(Bs + row * GEO::LD + ch * 4, src, in ? 16 : 0);
-    }
+    for (int u = 0; u < s.PB; ++u) cp_async16(Bs + u * s.RPP * GEO::LD, p.w + (size_t)(s.b[u] + kk), bytes);
 }
 
 // One k-tile of the (max, |a-b|) product for the 8 x TN sub-tile of this thread.
@@ -248,14 +265,20 @@ inf_forward_tiled_kernel(const TiledParams p) {
     const int col_off = wn * (8 * TN) + ln;      // + 8*j
 
     const int tiles_per_group = p.tiles_m * p.tiles_n;
-    long long u = unit_begin(p, blockIdx.x);
-    const long long u_end = unit_begin(p, blockIdx.x + 1);
+    // Work of this CTA, in units of one k-tile of one output tile.  Split mode (tickets set): an
+    // even share of all units, whatever tiles it cuts through.  Whole mode: output tiles
+    // blockIdx.x, blockIdx.x + n_cta, ... (the launcher gives every tile a CTA of its own: starting
+    // the CTAs of an SM staggered so that their rescans do not coincide was measured and lost,
+    // 215 us against 207 us at B = 512, Din = 784, Dout = 5120).
+    const bool whole = p.tickets == nullptr;
+    long long u = whole ? (long long)blockIdx.x * p.KT : unit_begin(p, blockIdx.x);
+    const long long u_end = whole ? (long long)tiles_per_group * p.G * p.KT : unit_begin(p, blockIdx.x + 1);
     int seg = 0;
 
     while (u < u_end) {
         const int tile = (int)(u / p.KT);
         const int kt0 = (int)(u - (long long)tile * p.KT);
-        const int kt1 = (int)min((long long)p.KT, kt0 + (u_end - u));
+        const int kt1 = whole ? p.KT : (int)min((long long)p.KT, kt0 + (u_end - u));
         const int g = tile / tiles_per_group;
         const int tg = tile - g * tiles_per_group;
         const int n0 = (tg / p.tiles_m) * BN, m0 = (tg % p.tiles_m) * BM;
@@ -269,10 +292,11 @@ inf_forward_tiled_kernel(const TiledParams p) {
         for (int e = 0; e < NB / 2; ++e) cid[e] = (unsigned)kt0 * 0x10001u;
 
         // ---- software pipeline over the k-tiles of this segment ----
+        const StageSrc<GEO> src = stage_src<GEO>(p, g, m0, n0, tid);
         __syncthreads();   // previous segment is done with the ring
 #pragma unroll
         for (int s = 0; s < STAGES - 1; ++s) {
-            if (kt0 + s < kt1) load_stage<GEO>(smem + s * STAGE_FLOATS, p, g, m0, n0, kt0 + s, tid);
+            if (kt0 + s < kt1) load_stage<GEO>(smem + s * STAGE_FLOATS, p, src, kt0 + s);
             cp_async_commit();
         }
         int rd = 0, wr = STAGES - 1;
@@ -289,7 +313,7 @@ inf_forward_tiled_kernel(const TiledParams p) {
                             cp_async_wait<STAGES - 2>();
                             __syncthreads();
                             if (ktc + STAGES - 1 < kt1)
-                                load_stage<GEO>(smem + wr * STAGE_FLOATS, p, g, m0, n0, ktc + STAGES - 1, tid);
+                                load_stage<GEO>(smem + wr * STAGE_FLOATS, p, src, ktc + STAGES - 1);
                             cp_async_commit();
                             const float* As = smem + rd * STAGE_FLOATS + row_off * GEO::LD;
                             const float* Bs = smem + rd * STAGE_FLOATS + (BM + col_off) * GEO::LD;
@@ -401,7 +425,7 @@ inf_forward_tiled_kernel(const TiledParams p) {
                 }
             }
         }
-        u += kt1 - kt0;
+        u += whole ? (long long)p.n_cta * p.KT : (long long)(kt1 - kt0);
         ++seg;   // only the first and the last segment of a CTA can be partial
     }
 }
@@ -437,7 +461,8 @@ int inf_forward_variant = 2;   // index into kVariants (benchmarking knob)
 // Shapes the tiled path accepts.
 static bool tiled_ok(const float* x, const float* w, const Dims& d) {
     return d.HW == 1 && (d.CIg % 4) == 0 && aligned16(x) && aligned16(w) &&
-           d.COg >= 32 && (d.CIg + 15) / 16 < 65536;
+           d.COg >= 32 && (d.CIg + 15) / 16 < 65536 &&
+           (size_t)d.R * d.CI < ((size_t)1 << 31) && (size_t)d.CO * d.CIg < ((size_t)1 << 31);
 }
 
 static const Variant& cur_variant() {
@@ -490,7 +515,7 @@ int inf_forward(const float* x, const float* w, const Dims& d, float* y, int* po
     p.KT = (d.CIg + v.bk - 1) / v.bk;
     const int tiles = p.tiles_m * p.tiles_n * d.G;
     p.tickets = nullptr; p.part_val = nullptr; p.part_cid = nullptr;
-    p.n_cta = tiles;
+    p.n_cta = tiles;       // whole mode: one CTA per output tile
     p.slots_cta = 0;
     const size_t need = inf_forward_workspace(d);
     if (ws != nullptr && need != 0) {
