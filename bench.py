@@ -321,8 +321,9 @@ def run_ours(args):
                 "peak_source": f"{props.multi_processor_count} SMs x 128 fp32 lanes x {sm_max:.0f} MHz "
                                "(sm_max_mhz of MEASURED_PEAKS.json; a max is not a multiply-add, so no tensor peak applies)",
                 "algorithmic": "2 fp32 non-FMA ops per term (1 subtract, 1 max-of-abs) x B*Din*Dout terms per launch",
-                "traffic": 22.3e6, "traffic_note": "dram read+write of one forward launch from the ncu capture "
-                           "summarised in profiles/ (compulsory: 17.7 MB in, 21 MB out, most writes still in L2)",
+                "traffic": 17.8e6, "traffic_note": "dram read+write of one forward launch from the ncu capture "
+                           "summarised in profiles/ (compulsory: 17.7 MB in, 21 MB out; the outputs are still in L2 "
+                           "when the launch ends)",
                 "backward_hbm": {"bound": "hbm", "achieved": bwd_bytes / (t_bwd * 1e-3) / 1e9, "peak": hbm_peak,
                                  "unit": "GB/s", "frac": bwd_bytes / (t_bwd * 1e-3) / 1e9 / hbm_peak},
             },
