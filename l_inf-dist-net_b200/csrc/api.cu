@@ -22,6 +22,7 @@ int sm_count() {
 }
 
 extern int inf_forward_variant;
+int inf_forward_tma_gave_up();
 
 }  // namespace linf
 
@@ -55,6 +56,7 @@ const char* linf_error_string(int code) {
 // surface; not thread safe.
 int linf_tune_set(int key, int value) {
     if (key == 0 && value >= 0 && value < 16) { inf_forward_variant = value; return LINF_OK; }
+    if (key == 2) return inf_forward_tma_gave_up();   // 1 = a bounded wait of the TMA loader ran out since the library was loaded
     return LINF_ERR_DIMS;
 }
 

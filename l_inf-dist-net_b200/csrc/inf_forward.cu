@@ -19,6 +19,8 @@
 //     CTAs arrives last (ticket counter, nobody waits).
 //   * few outputs per group (skinny.cu): the reduction is spread over the threads of a CTA.
 //   * generic path (any G, HW, alignment): 32 x 32 tile, index tracked per term.
+#include <cuda.h>   // CUtensorMap and the enums of cuTensorMapEncodeTiled (types only: no libcuda link)
+
 #include "common.cuh"
 
 namespace linf {
@@ -111,6 +113,7 @@ struct TiledParams {
     int* tickets;          // one counter per output tile (split mode), else nullptr
     float* part_val;       // [slots_cta][2][TILE_OUT]
     int* part_cid;         // [slots_cta][2][TILE_OUT]
+    CUtensorMap tm_x, tm_w; // TMA loader only: x as [R][CI], w as [CO][CIg], boxes of (BK + 4) x 64 floats
 };
 
 __device__ __forceinline__ long long unit_begin(const TiledParams& p, int c) {
@@ -250,16 +253,78 @@ __device__ __forceinline__ int resolve_pos(const float* __restrict__ xrow, const
     return (kbase + best) | (tb < 0.f ? (int)0x80000000 : 0);
 }
 
-template <class GEO, int MODE, bool TRACK>
+// ---- TMA loader (LOADER == 1) ---------------------------------------------------------------
+// One thread per CTA issues two tiled bulk copies per k-tile: (BK + 4) x BM floats of x and
+// (BK + 4) x BN floats of w.  The four extra columns are fetched only so that the rows land in
+// shared memory with the same 20-float pitch the cp.async loader produces (conflict-free 128-bit
+// fragment loads without a swizzle); out-of-range rows and columns arrive as zeros.  Completion is
+// signalled on one mbarrier per stage; every wait is bounded: a thread that gives up sets
+// g_tma_gave_up, marks the CTA dead (later waits return at once) and the launch finishes with
+// meaningless results instead of hanging.
+__device__ int g_tma_gave_up = 0;
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, int bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, int parity) {
+    unsigned ok;
+    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void mbar_wait(unsigned long long* bar, int parity, volatile int* dead) {
+    if (mbar_try_wait(bar, parity)) return;
+    if (*dead) return;
+    for (int spin = 0; spin < (1 << 20); ++spin)
+        if (mbar_try_wait(bar, parity)) return;
+    *dead = 1;
+    atomicExch(&g_tma_gave_up, 1);
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* tm, int c0, int c1, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_u32(dst)), "l"(tm), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+
+// One thread fills a stage: the x box at (column xc, row xr) and the w box at (column wc, row wr).
+template <class GEO>
+__device__ __forceinline__ void tma_stage(float* stage, unsigned long long* bar, const CUtensorMap* tm_x,
+                                          const CUtensorMap* tm_w, int xc, int xr, int wc, int wr, int tid) {
+    if (tid == 0) {
+        mbar_expect_tx(bar, GEO::STAGE_FLOATS * 4);
+        tma_load_2d(stage, tm_x, xc, xr, bar);
+        tma_load_2d(stage + GEO::BM * GEO::LD, tm_w, wc, wr, bar);
+    }
+}
+
+template <class GEO, int MODE, bool TRACK, int LOADER>
 __global__ void __launch_bounds__(GEO::NT, GEO::MINB)
-inf_forward_tiled_kernel(const TiledParams p) {
+inf_forward_tiled_kernel(const __grid_constant__ TiledParams p) {
     constexpr int NT = GEO::NT, TN = GEO::TN, NOUT = GEO::NOUT, BK = GEO::BK, TILE_OUT = GEO::TILE_OUT;
     constexpr int BM = GEO::BM, BN = GEO::BN, STAGES = GEO::STAGES, STAGE_FLOATS = GEO::STAGE_FLOATS;
     constexpr int NB = TRACK ? NOUT : 2;        // size of the second accumulator set / tile-number set
-    extern __shared__ __align__(16) float smem[];
+    extern __shared__ __align__(16) float smem_raw[];
     __shared__ int s_last;
+    __shared__ int s_dead;
+    __shared__ __align__(8) unsigned long long s_full[STAGES];   // TMA loader: "stage filled" barriers
+    // TMA writes want a 128-byte aligned destination: the launcher reserves 128 bytes for the round-up
+    float* smem = LOADER == 1
+        ? reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t)127) : smem_raw;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if constexpr (LOADER == 1) {
+        if (tid == 0) {
+            s_dead = 0;
+#pragma unroll
+            for (int s = 0; s < STAGES; ++s) mbar_init(&s_full[s], 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        __syncthreads();
+    }
+    [[maybe_unused]] unsigned filled = 0;   // TMA loader: k-tiles consumed so far (stage = filled % STAGES, parity from filled / STAGES)
     const int wm = warp & 1, wn = warp >> 1, lm = lane >> 3, ln = lane & 7;
     const int row_off = wm * 32 + lm;            // + 4*i
     const int col_off = wn * (8 * TN) + ln;      // + 8*j
@@ -294,12 +359,21 @@ inf_forward_tiled_kernel(const TiledParams p) {
         // ---- software pipeline over the k-tiles of this segment ----
         const StageSrc<GEO> src = stage_src<GEO>(p, g, m0, n0, tid);
         __syncthreads();   // previous segment is done with the ring
+        int rd = 0, wr = STAGES - 1;
+        if constexpr (LOADER == 1) {
+            // the ring position carries over from segment to segment (the barriers' phases depend on it)
+            rd = (int)(filled % STAGES); wr = (rd + STAGES - 1) % STAGES;
+        }
 #pragma unroll
         for (int s = 0; s < STAGES - 1; ++s) {
-            if (kt0 + s < kt1) load_stage<GEO>(smem + s * STAGE_FLOATS, p, src, kt0 + s);
-            cp_async_commit();
+            if constexpr (LOADER == 0) {
+                if (kt0 + s < kt1) load_stage<GEO>(smem + s * STAGE_FLOATS, p, src, kt0 + s);
+                cp_async_commit();
+            } else {
+                if (kt0 + s < kt1) tma_stage<GEO>(smem + ((rd + s) % STAGES) * STAGE_FLOATS, &s_full[(rd + s) % STAGES],
+                                                  &p.tm_x, &p.tm_w, g * p.K + (kt0 + s) * BK, m0, (kt0 + s) * BK, g * p.N + n0, tid);
+            }
         }
-        int rd = 0, wr = STAGES - 1;
         constexpr int TRK = GEO::TRK;
         for (int kt = kt0; kt < kt1; kt += 2 * TRK) {
 #pragma unroll
@@ -310,11 +384,22 @@ inf_forward_tiled_kernel(const TiledParams p) {
                     for (int s2 = 0; s2 < TRK; ++s2) {
                         const int ktc = kb + s2;
                         if (ktc < kt1) {
-                            cp_async_wait<STAGES - 2>();
-                            __syncthreads();
-                            if (ktc + STAGES - 1 < kt1)
-                                load_stage<GEO>(smem + wr * STAGE_FLOATS, p, src, ktc + STAGES - 1);
-                            cp_async_commit();
+                            if constexpr (LOADER == 0) {
+                                cp_async_wait<STAGES - 2>();
+                            } else {
+                                mbar_wait(&s_full[rd], (int)((filled / STAGES) & 1u), &s_dead);
+                                ++filled;
+                            }
+                            __syncthreads();   // every thread is done with the stage about to be refilled
+                            if constexpr (LOADER == 0) {
+                                if (ktc + STAGES - 1 < kt1)
+                                    load_stage<GEO>(smem + wr * STAGE_FLOATS, p, src, ktc + STAGES - 1);
+                                cp_async_commit();
+                            } else {
+                                if (ktc + STAGES - 1 < kt1)
+                                    tma_stage<GEO>(smem + wr * STAGE_FLOATS, &s_full[wr], &p.tm_x, &p.tm_w,
+                                                   g * p.K + (ktc + STAGES - 1) * BK, m0, (ktc + STAGES - 1) * BK, g * p.N + n0, tid);
+                            }
                             const float* As = smem + rd * STAGE_FLOATS + row_off * GEO::LD;
                             const float* Bs = smem + rd * STAGE_FLOATS + (BM + col_off) * GEO::LD;
                             if constexpr (TRACK) {
@@ -345,7 +430,7 @@ inf_forward_tiled_kernel(const TiledParams p) {
                 }
             }
         }
-        cp_async_wait<0>();
+        if constexpr (LOADER == 0) cp_async_wait<0>();
 
         // ---- finish the segment ----
         const bool complete = (kt0 == 0 && kt1 == p.KT);
@@ -435,14 +520,15 @@ size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 // ---- variant table ------------------------------------------------------------------------
 struct Variant {
     int bm, bn, bk, nt, min_blocks, smem;
+    bool tma;
     void (*kern_track)(const TiledParams);
     void (*kern_plain)(const TiledParams);
 };
 
-template <class GEO, int MODE>
+template <class GEO, int MODE, int LOADER = 0>
 constexpr Variant make_variant() {
-    return Variant{GEO::BM, GEO::BN, GEO::BK, GEO::NT, GEO::MINB, GEO::SMEM_BYTES,
-                   inf_forward_tiled_kernel<GEO, MODE, true>, inf_forward_tiled_kernel<GEO, MODE, false>};
+    return Variant{GEO::BM, GEO::BN, GEO::BK, GEO::NT, GEO::MINB, GEO::SMEM_BYTES + (LOADER == 1 ? 128 : 0), LOADER == 1,
+                   inf_forward_tiled_kernel<GEO, MODE, true, LOADER>, inf_forward_tiled_kernel<GEO, MODE, false, LOADER>};
 }
 
 const Variant kVariants[] = {
@@ -451,10 +537,20 @@ const Variant kVariants[] = {
     make_variant<Geo<128, 4, 16, 3>, 2>(),   // 2: 8x4 per thread, 128 threads (64x64 tile), 3 CTAs/SM (default)
     make_variant<Geo<128, 4, 16, 3>, 0>(),   // 3: as 2 with scalar subtract + 2-input max
     make_variant<Geo<128, 4, 16, 3>, 1>(),   // 4: as 2 with scalar subtract + 3-input max
+    make_variant<Geo<128, 4, 16, 3>, 2, 1>(),// 5: as 2 with the TMA loader (measured 7-14 % slower than 2: the extra four
+                                             //    columns per row cost L2 traffic and one thread issues every copy)
 };
 constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
 
 }  // namespace
+
+// Reads the flag a TMA-loader kernel sets when one of its bounded waits ran out (diagnostics only:
+// synchronises the device).
+int inf_forward_tma_gave_up() {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tma_gave_up, sizeof(int)) != cudaSuccess) return -1;
+    return v;
+}
 
 int inf_forward_variant = 2;   // index into kVariants (benchmarking knob)
 
@@ -496,6 +592,45 @@ size_t inf_forward_workspace(const Dims& d) {
            n_cta * 2 * v.bm * v.bn * (sizeof(float) + sizeof(int));
 }
 
+// ---- tensor maps for the TMA loader ----------------------------------------------------------
+// cuTensorMapEncodeTiled is a host-only driver routine; it is looked up through the runtime so
+// that the library does not link libcuda.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn tma_encoder() {
+    static EncodeTiledFn fn = [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            f = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(f);
+    }();
+    return fn;
+}
+
+// A row-major fp32 matrix [rows][cols] with `pitch` floats between rows, fetched in boxes of
+// box_cols x box_rows.  The rules of the copy engine: base and pitch multiples of 16 bytes, box
+// width a multiple of 16 bytes; the kernel only ever starts a box at a column that is a multiple
+// of 16 floats.
+static bool tma_matrix(const float* base, size_t rows, size_t cols, size_t pitch, int box_cols, int box_rows,
+                       CUtensorMap* out) {
+    EncodeTiledFn fn = tma_encoder();
+    if (fn == nullptr || (reinterpret_cast<uintptr_t>(base) & 15u) || (pitch & 3u) || (box_cols & 3)) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)pitch * sizeof(float)};
+    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    return fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// The TMA loader zero-fills past the END OF A ROW OF THE MATRIX.  With groups the k-tiles of one
+// group are followed by the next group's columns, so a ragged last k-tile is only right for G = 1.
+static bool tma_shape_ok(const Dims& d) { return (d.G == 1 || d.CIg % 16 == 0) && d.CIg >= 32 && d.R >= 1; }
+
 int inf_forward(const float* x, const float* w, const Dims& d, float* y, int* pos,
                 void* ws, size_t ws_bytes, cudaStream_t st) {
     if (!tiled_ok(x, w, d)) {
@@ -529,12 +664,19 @@ int inf_forward(const float* x, const float* w, const Dims& d, float* y, int* po
         p.part_cid = reinterpret_cast<int*>(p.part_val + (size_t)p.slots_cta * 2 * v.bm * v.bn);
         if (cudaMemsetAsync(p.tickets, 0, tick_bytes, st) != cudaSuccess) return LINF_ERR_LAUNCH;
     }
-    auto kern = pos != nullptr ? v.kern_track : v.kern_plain;
+    const Variant* use = &v;
+    if (v.tma) {
+        const bool ok = tma_shape_ok(d) &&
+                        tma_matrix(x, (size_t)d.R, (size_t)d.CI, (size_t)d.CI, v.bk + 4, v.bm, &p.tm_x) &&
+                        tma_matrix(w, (size_t)d.CO, (size_t)d.CIg, (size_t)d.CIg, v.bk + 4, v.bn, &p.tm_w);
+        if (!ok) use = &kVariants[2];           // same geometry with the cp.async loader
+    }
+    auto kern = pos != nullptr ? use->kern_track : use->kern_plain;
     // opting in to > 48 KB of dynamic shared memory is per function and per device; it is cheap
     // enough to repeat on every call and keeps the library free of mutable global state
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, v.smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, use->smem) != cudaSuccess)
         return LINF_ERR_LAUNCH;
-    kern<<<p.n_cta, v.nt, v.smem, st>>>(p);
+    kern<<<p.n_cta, use->nt, use->smem, st>>>(p);
     return launch_status();
 }
 

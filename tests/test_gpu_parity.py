@@ -492,3 +492,23 @@ def test_inf_backward_synthetic_positions(cuda, lib, pattern, shape):
     for mode in ("ordered", "both"):
         gx, gw = c_inf_backward(dev(g), dev(pos), CI, G, mode)
         assert_bits_equal(gx, gx_ref, f"{mode} grad_input"); assert_bits_equal(gw, gw_ref, f"{mode} grad_weight")
+
+
+@pytest.mark.parametrize("shape", [(64, 64, 64, 1, 1), (33, 100, 65, 1, 1), (130, 784, 200, 1, 1), (16, 64, 256, 1, 4),
+                                   (70, 1000, 96, 1, 1), (512, 784, 640, 1, 1), (64, 3072, 512, 1, 4), (9, 36, 40, 1, 1)], ids=_ids)
+def test_inf_forward_tma_loader_variant(cuda, lib, shape):
+    """The same tiled kernel with its operand tiles fetched by TMA (tiled bulk copies, completion on
+    mbarriers) instead of cp.async: a build option that is not the default (it measured slower), kept
+    bit-identical.  Ragged k-tiles, rows and channels past the end arrive as zeros from the copy engine;
+    the bounded waits must never have run out."""
+    B, CI, CO, HW, G = shape
+    x, w, _ = make_inputs(B, CI, CO, HW, G, seed=77 + CI)
+    y_ref, pos_ref = oracle.inf_dist_forward(x, w, G)
+    assert lib.linf_tune_set(0, 5) == 0
+    try:
+        for use_ws in (False, True):
+            y, pos = c_inf_forward(dev(x), dev(w), G, use_ws=use_ws)
+            assert_bits_equal(y, y_ref, "values"); assert_bits_equal(pos, pos_ref, "arg-max")
+        assert lib.linf_tune_set(2, 0) == 0
+    finally:
+        lib.linf_tune_set(0, 2)
