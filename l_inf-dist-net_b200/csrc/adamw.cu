@@ -121,6 +121,69 @@ adamw_rows_kernel(const AdamArgs a) {
     }
 }
 
+
+// p_norm = inf with rows that are a multiple of 4 floats long and 16-byte aligned: the same
+// arithmetic with 128-bit accesses, four times the bytes in flight per thread (the scalar kernel
+// reaches ~60 % of the measured copy bandwidth on 5120 x 5120 weights, bound by latency).
+__global__ void __launch_bounds__(256)
+adamw_rows_inf_vec4_kernel(const AdamArgs a) {
+    extern __shared__ __align__(16) float row_s[];
+    __shared__ float red[8];
+    __shared__ int red_i[8];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const size_t base = (size_t)blockIdx.x * a.cols;
+    const int c4n = a.cols >> 2;
+    float4* x4 = reinterpret_cast<float4*>(a.param + base);
+    float4* rs4 = reinterpret_cast<float4*>(row_s);
+
+    float best = -1.f; int bi = 0x7fffffff;
+    for (int c = tid; c < c4n; c += 256) {
+        const float4 v = x4[c];
+        rs4[c] = v;
+        float av;
+        av = fabsf(v.x); if (av > best) { best = av; bi = 4 * c; }
+        av = fabsf(v.y); if (av > best) { best = av; bi = 4 * c + 1; }
+        av = fabsf(v.z); if (av > best) { best = av; bi = 4 * c + 2; }
+        av = fabsf(v.w); if (av > best) { best = av; bi = 4 * c + 3; }
+    }
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) {
+        const float b2 = __shfl_xor_sync(0xffffffffu, best, s);
+        const int i2 = __shfl_xor_sync(0xffffffffu, bi, s);
+        if (b2 > best || (b2 == best && i2 < bi)) { best = b2; bi = i2; }
+    }
+    if (lane == 0) { red[warp] = best; red_i[warp] = bi; }
+    __syncthreads();
+    best = red[0]; bi = red_i[0];
+    for (int w = 1; w < 8; ++w)
+        if (red[w] > best || (red[w] == best && red_i[w] < bi)) { best = red[w]; bi = red_i[w]; }
+    const int k_star = bi;         // lowest index among equal magnitudes
+
+    const float one_b1 = 1.f - a.beta1, one_b2 = 1.f - a.beta2;
+    const float4* g4 = reinterpret_cast<const float4*>(a.grad + base);
+    float4* m4 = reinterpret_cast<float4*>(a.m + base);
+    float4* v4 = reinterpret_cast<float4*>(a.v + base);
+    auto upd = [&](float xv, float g, float& m, float& v, bool decays) {
+        if (decays) xv += -a.lr_wd * xv;
+        m = a.beta1 * m + one_b1 * g;
+        v = a.beta2 * v + one_b2 * g * g;
+        const float denom = sqrtf(v) * a.inv_sqrt_bc2 + a.eps;
+        return xv - a.step_size * (m / denom);
+    };
+#pragma unroll 2
+    for (int c = tid; c < c4n; c += 256) {
+        float4 xv = rs4[c];
+        const float4 g = g4[c];
+        float4 m = m4[c], v = v4[c];
+        const int kk = k_star - 4 * c;      // 0..3 when the decaying column is in this quad
+        xv.x = upd(xv.x, g.x, m.x, v.x, kk == 0);
+        xv.y = upd(xv.y, g.y, m.y, v.y, kk == 1);
+        xv.z = upd(xv.z, g.z, m.z, v.z, kk == 2);
+        xv.w = upd(xv.w, g.w, m.w, v.w, kk == 3);
+        m4[c] = m; v4[c] = v; x4[c] = xv;
+    }
+}
+
 }  // namespace
 }  // namespace linf
 
@@ -152,7 +215,15 @@ extern "C" int linf_adamw_step(float* param, const float* grad, float* exp_avg, 
         }
     } else if (mode == 1) {
         if (smem > 40 * 1024 && cudaFuncSetAttribute(adamw_rows_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return LINF_ERR_LAUNCH;
-        adamw_rows_kernel<1><<<rows, 256, smem, st>>>(a);
+        const bool vec = (cols & 3) == 0 &&
+                         ((reinterpret_cast<uintptr_t>(param) | reinterpret_cast<uintptr_t>(grad) |
+                           reinterpret_cast<uintptr_t>(exp_avg) | reinterpret_cast<uintptr_t>(exp_avg_sq)) & 15u) == 0;
+        if (vec) {
+            if (smem > 40 * 1024 && cudaFuncSetAttribute(adamw_rows_inf_vec4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return LINF_ERR_LAUNCH;
+            adamw_rows_inf_vec4_kernel<<<rows, 256, smem, st>>>(a);
+        } else {
+            adamw_rows_kernel<1><<<rows, 256, smem, st>>>(a);
+        }
     } else {
         if (smem > 40 * 1024 && cudaFuncSetAttribute(adamw_rows_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return LINF_ERR_LAUNCH;
         adamw_rows_kernel<2><<<rows, 256, smem, st>>>(a);
