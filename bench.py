@@ -312,11 +312,11 @@ def run_ours(args):
     if not args.no_train:
         try:
             from linfdist_b200.train_step import bench_train_step
-            train = bench_train_step(dev, world, rank, steps=args.train_steps, warmup=3)
+            train = bench_train_step(dev, world, rank, steps=args.train_steps, warmup=5)
         except Exception as exc:                                           # never lose the layer line
             train = {"error": repr(exc)}
         try:
-            train_tiny = bench_train_step(dev, world, rank, steps=args.train_steps, warmup=3, config="tiny")
+            train_tiny = bench_train_step(dev, world, rank, steps=args.train_steps, warmup=5, config="tiny")
         except Exception as exc:
             train_tiny = {"error": repr(exc)}
 

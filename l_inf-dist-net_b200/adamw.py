@@ -65,6 +65,34 @@ class AdamW(Optimizer):
             if p.grad is not None:
                 self._update(p, self._group_of[id(p)])
 
+    @torch.no_grad()
+    def step_rows(self, p, row0, nrows, grad_rows):
+        """Updates rows [row0, row0 + nrows) of the CUDA parameter `p` from `grad_rows` (their
+        gradient, [nrows, cols], contiguous).  The moment estimates of these rows live in tensors of
+        their own, so a data-parallel driver that shards the optimiser keeps only its share of the
+        state.  The row-wise decay rule makes whole rows the natural shard."""
+        if not hasattr(self, "_group_of"):
+            self._group_of = {id(q): g for g in self.param_groups for q in g["params"]}
+        group = self._group_of[id(p)]
+        beta1, beta2 = group["betas"]
+        state = self.state[p]
+        key = ("rows", row0, nrows)
+        if key not in state:
+            state[key] = {"step": 0, "exp_avg": torch.zeros_like(grad_rows), "exp_avg_sq": torch.zeros_like(grad_rows)}
+        st = state[key]
+        st["step"] += 1
+        p_norm = get_p_norm(group["module"])
+        cols = p.numel() // p.size(0)
+        if not (p.is_cuda and p.dtype == torch.float32 and p.is_contiguous() and grad_rows.is_contiguous()
+                and grad_rows.dtype == torch.float32 and cols <= 51200):
+            raise RuntimeError("step_rows needs a contiguous fp32 CUDA parameter with rows of at most 51200 entries")
+        with torch.cuda.device(p.device):
+            rc = _lib.load().linf_adamw_step(
+                p.data_ptr() + row0 * cols * 4, grad_rows.data_ptr(), st["exp_avg"].data_ptr(), st["exp_avg_sq"].data_ptr(),
+                nrows, cols, -1.0 if p_norm is None else float(p_norm), group["lr"], beta1, beta2,
+                group["eps"], group["weight_decay"], st["step"], torch.cuda.current_stream().cuda_stream)
+        _lib.check(rc, "adamw_step")
+
     def _update(self, p, group):
         if p.grad.is_sparse:
             raise RuntimeError("AdamW does not support sparse gradients")

@@ -91,13 +91,12 @@ class DataParallelStep:
         self.buffers = list(net.buffers()) if self.world > 1 else []
         self.events = {}
         self.sent, self.held = 0, []
-        for p in self.params:
-            p.register_post_accumulate_grad_hook(self._on_grad)
+        self.handles = [p.register_post_accumulate_grad_hook(self._on_grad) for p in self.params]
         if self.cuda:
             for m in net.modules():
                 own = [q for q in m.parameters(recurse=False) if q.requires_grad]
                 if own:
-                    m.register_forward_pre_hook(self._make_wait(own))
+                    self.handles.append(m.register_forward_pre_hook(self._make_wait(own)))
 
     def _make_wait(self, own):
         def wait(module, inputs):
@@ -163,6 +162,166 @@ class DataParallelStep:
         if self.cuda:
             torch.cuda.current_stream().wait_stream(self.side)
 
+    def close(self):
+        """Takes the hooks off the network (the hooks hold this object, the object holds the network)."""
+        for h in self.handles:
+            h.remove()
+        self.handles = []
+
+
+class ShardedCopyEngineStep(DataParallelStep):
+    """Data-parallel step for one replica per GPU on an NVLink/NVSwitch node in which the gradient
+    exchange of the large weight matrices uses no SM at all:
+
+      * every large parameter (rows divisible by the world size) lives in symmetric memory, so that
+        peers can write into it; rank r owns rows [r*s, (r+1)*s) of it together with the Adam moments
+        of those rows only (the optimiser state and work are sharded, the row-wise l_p decay makes
+        rows the natural unit);
+      * when the gradient of such a parameter is ready, rank r PUSHES chunk j of it into a staging
+        area on rank j with peer-to-peer copies (copy engines over NVLink) and then raises a flag in
+        rank j's memory with a stream memory operation; rank r waits -- again with stream memory
+        operations, not kernels -- for the W-1 chunks addressed to it, adds the W chunks in rank
+        order, divides by W, runs the fused optimiser kernel on its rows and pushes the updated rows
+        into every peer's copy of the parameter, raising a second flag;
+      * the next forward waits, layer by layer, for its own update and the W-1 flags of that layer.
+
+    Why not NCCL here: the forward kernels of the wide layers fill every SM for hundreds of
+    microseconds per CTA, so a collective kernel launched while they run starts only when they
+    end; with all-reduce kernels the exchange of the layers that finish their backward last ends up
+    exposed (6.3 ms per step on 8 GPUs against 5.0 ms on one).  Copies and flag operations need no
+    SM and run under the forward pass.  Small parameters (biases) keep the NCCL all-reduce of the
+    base class.  Every shard is reduced by exactly one rank in a fixed order and then copied, so all
+    replicas hold bit-identical parameters.
+
+    A rank that dies leaves its peers waiting on a flag (as a dead rank leaves NCCL waiting): run it
+    under a job-level timeout."""
+
+    MIN_BYTES = 1 << 20
+
+    def __init__(self, net, optimizer):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        from cuda.bindings import driver as cu
+        super().__init__(net, optimizer)
+        if not (self.cuda and self.world > 1):
+            raise RuntimeError("ShardedCopyEngineStep needs CUDA tensors and more than one rank")
+        self.cu = cu
+        self.rank = dist.get_rank()
+        self.copy = torch.cuda.Stream()      # gradient chunks to their owners
+        self.push = torch.cuda.Stream()      # updated rows to every replica
+        group = dist.group.WORLD.group_name
+        W, r = self.world, self.rank
+        self.big = {}
+        for p in self.params:
+            if p.dim() < 2 or p.size(0) % W or p.numel() * 4 < self.MIN_BYTES:
+                continue
+            rows, cols = p.size(0), p.numel() // p.size(0)
+            s = rows // W
+            store = symm_mem.empty(p.numel(), dtype=torch.float32, device=p.device)
+            stage = symm_mem.empty(p.numel(), dtype=torch.float32, device=p.device)      # [W][s * cols]
+            flags = symm_mem.empty(2 * W, dtype=torch.int32, device=p.device)
+            flags.zero_()
+            store.copy_(p.data.reshape(-1))
+            hs, hg, hf = (symm_mem.rendezvous(t, group) for t in (store, stage, flags))
+            p.data = store.view(p.shape)
+            self.big[id(p)] = {
+                "rows": rows, "cols": cols, "s": s, "step": 0, "others": [(r + k) % W for k in range(1, W)],
+                "store": store.view(rows, cols), "stage": stage.view(W, s * cols), "flags": flags,
+                "peer_store": [hs.get_buffer(j, (rows, cols), torch.float32) for j in range(W)],
+                "peer_stage": [hg.get_buffer(j, (W, s * cols), torch.float32) for j in range(W)],
+                "peer_flags": [hf.get_buffer(j, (2 * W,), torch.int32) for j in range(W)],
+                "reduced": torch.empty(s, cols, dtype=torch.float32, device=p.device),
+                "updated": torch.cuda.Event(), "pushed": torch.cuda.Event(),
+            }
+        torch.cuda.synchronize()
+        dist.barrier()
+
+    # ---- stream memory operations and peer copies through the driver API (no kernel, no SM; one
+    # driver call per group of flags keeps the host cost of a step low) ----
+    def _flag_ops(self, stream, wait, tensors_indices, value):
+        cu = self.cu
+        ops = []
+        for tensor, index in tensors_indices:
+            op = cu.CUstreamBatchMemOpParams()
+            if wait:
+                op.operation = cu.CUstreamBatchMemOpType.CU_STREAM_MEM_OP_WAIT_VALUE_32
+                op.waitValue.operation = cu.CUstreamBatchMemOpType.CU_STREAM_MEM_OP_WAIT_VALUE_32
+                op.waitValue.address = tensor.data_ptr() + 4 * index
+                op.waitValue.value = value
+                op.waitValue.flags = int(cu.CUstreamWaitValue_flags.CU_STREAM_WAIT_VALUE_GEQ)
+            else:
+                op.operation = cu.CUstreamBatchMemOpType.CU_STREAM_MEM_OP_WRITE_VALUE_32
+                op.writeValue.operation = cu.CUstreamBatchMemOpType.CU_STREAM_MEM_OP_WRITE_VALUE_32
+                op.writeValue.address = tensor.data_ptr() + 4 * index
+                op.writeValue.value = value
+                op.writeValue.flags = 0
+            ops.append(op)
+        rc = cu.cuStreamBatchMemOp(cu.CUstream(stream.cuda_stream), len(ops), ops, 0)
+        if rc[0] != cu.CUresult.CUDA_SUCCESS:
+            raise RuntimeError("cuStreamBatchMemOp: %s" % (rc[0],))
+
+    def _push(self, stream, dst, src):
+        """Asynchronous copy of `src` (local) into `dst` (a view of a peer's symmetric memory)."""
+        rc = self.cu.cuMemcpyAsync(self.cu.CUdeviceptr(dst.data_ptr()), self.cu.CUdeviceptr(src.data_ptr()),
+                                   src.numel() * src.element_size(), self.cu.CUstream(stream.cuda_stream))
+        if rc[0] != self.cu.CUresult.CUDA_SUCCESS:
+            raise RuntimeError("cuMemcpyAsync: %s" % (rc[0],))
+
+    def _make_wait(self, own):
+        base = super()._make_wait(own)
+
+        def wait(module, inputs):
+            base(module, inputs)
+            cur = torch.cuda.current_stream()
+            for q in own:
+                b = self.big.get(id(q))
+                if b is not None and b["step"] > 0:
+                    cur.wait_event(b["updated"])
+                    self._flag_ops(cur, True, [(b["flags"], self.world + j) for j in b["others"]], b["step"])
+        return wait
+
+    def _issue(self, p):
+        b = self.big.get(id(p))
+        if b is None:
+            return super()._issue(p)
+        W, r, s, cols = self.world, self.rank, b["s"], b["cols"]
+        b["step"] += 1
+        t = b["step"]
+        grad = p.grad.view(W, s * cols)
+        ready = torch.cuda.Event()
+        ready.record(torch.cuda.current_stream())
+        p.grad.record_stream(self.copy)
+        p.grad.record_stream(self.side)
+        # 1. chunks of this rank's gradient to their owners, then the "chunk from r has landed" flags
+        self.copy.wait_event(ready)
+        for j in b["others"]:                     # starts with the right-hand neighbour: spreads the load
+            self._push(self.copy, b["peer_stage"][j][r], grad[j])
+        self._flag_ops(self.copy, False, [(b["peer_flags"][j], r) for j in b["others"]], t)
+        # 2. own shard: wait for the W-1 chunks, add in rank order, average, update the rows
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(ready)
+            if t > 1:
+                self.side.wait_event(b["pushed"])     # last step's pushes have read the rows about to change
+            b["stage"][r].copy_(grad[r], non_blocking=True)
+            self._flag_ops(self.side, True, [(b["flags"], j) for j in b["others"]], t)
+            torch.sum(b["stage"].view(W, s, cols), dim=0, out=b["reduced"])
+            b["reduced"].mul_(1.0 / W)
+            self.opt.step_rows(p, r * s, s, b["reduced"])
+            b["updated"].record(self.side)
+        # 3. the updated rows to every replica, on a stream of their own so that the next
+        #    parameter's reduction does not queue behind these copies
+        self.push.wait_event(b["updated"])
+        mine = b["store"][r * s:(r + 1) * s]
+        for j in b["others"]:
+            self._push(self.push, b["peer_store"][j][r * s:(r + 1) * s], mine)
+        self._flag_ops(self.push, False, [(b["peer_flags"][j], W + r) for j in b["others"]], t)
+        b["pushed"].record(self.push)
+
+    def synchronize(self):
+        super().synchronize()
+        torch.cuda.current_stream().wait_stream(self.copy)
+        torch.cuda.current_stream().wait_stream(self.push)
+
 
 def bench_train_step(device, world, rank, steps=8, warmup=3, batch=None, p=float("inf"), config="cifar"):
     """Times `steps` optimisation steps (after `warmup`), inputs copied from pinned host memory
@@ -186,15 +345,51 @@ def bench_train_step(device, world, rank, steps=8, warmup=3, batch=None, p=float
         side, classes = 64, 200
         what = ("MLPFeature 12288-5120x5 + head 5120-512(tanh)-200, MeanNorm, eps 1/255, cross entropy, "
                 "fused AdamW lr .04 wd 5e-3")
-    model = DataParallelStep(net, opt)
+    exchange = "one NCCL all-reduce (avg) per parameter issued as its gradient is ready, optimiser applied per parameter as it arrives"
+    model = None
+    if world > 1 and device.type == "cuda":
+        import os
+        if os.environ.get("LINF_EXCHANGE", "copy") == "copy":
+            try:
+                model = ShardedCopyEngineStep(net, opt)
+                exchange = ("weight gradients pushed shard by shard over NVLink by the copy engines, flags by stream memory "
+                            "operations, optimiser sharded by rows, updated rows pushed back (no SM used by the exchange); "
+                            "biases by NCCL all-reduce")
+            except Exception as exc:                   # no symmetric memory on this system: NCCL path
+                exchange += " (copy-engine exchange unavailable: %r)" % (exc,)
+    if model is None:
+        model = DataParallelStep(net, opt)
     gen = torch.Generator().manual_seed(4040 + rank)
     images = torch.rand(batch, 3, side, side, generator=gen).pin_memory()
     labels = torch.randint(0, classes, (batch,), generator=gen).pin_memory()
     net.train()
 
+    # Every step copies its batch from pinned host memory; the copy of the NEXT batch is issued on a
+    # stream of its own at the start of a step, so that it runs under this step's kernels instead of
+    # in front of the first layer (with the copy-engine exchange it would otherwise also queue behind
+    # the last parameter pushes of the previous step).
+    h2d = torch.cuda.Stream() if device.type == "cuda" else None
+    nxt = {}
+
+    def fetch():
+        if h2d is None:
+            nxt["x"], nxt["t"], nxt["ev"] = images.to(device), labels.to(device), None
+            return
+        with torch.cuda.stream(h2d):
+            nxt["x"] = images.to(device, non_blocking=True)
+            nxt["t"] = labels.to(device, non_blocking=True)
+            nxt["ev"] = torch.cuda.Event()
+            nxt["ev"].record(h2d)
+
+    fetch()
+
     def step():
-        x = images.to(device, non_blocking=True)
-        t = labels.to(device, non_blocking=True)
+        x, t, ev = nxt["x"], nxt["t"], nxt["ev"]
+        if ev is not None:
+            cur = torch.cuda.current_stream()
+            cur.wait_event(ev)
+            x.record_stream(cur); t.record_stream(cur)
+        fetch()
         outputs, worst = model(x, targets=t)
         loss = loss_fn(outputs, worst, t)
         opt.zero_grad(set_to_none=True)
@@ -223,10 +418,16 @@ def bench_train_step(device, world, rank, steps=8, warmup=3, batch=None, p=float
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     params = sum(q.numel() for q in net.parameters())
+    # give the memory of this leg back before the next one (another model in the same process)
+    model.close()
+    del model, opt, loss
+    if device.type == "cuda":
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
     name = "CIFAR-shape L_inf-dist net" if config == "cifar" else "TinyImageNet-shape L_inf-dist net+MLP"
     return {"metric": name + " train samples/s", "value": world * batch / (ms * 1e-3),
             "unit": "samples/s", "ms_per_step": ms, "steps": steps, "batch_per_gpu": batch, "n_gpus": world,
             "p": "inf" if math.isinf(p) else p, "loss": last, "parameters": params,
             "config": what + "; "
-                      "n_gpus > 1: data parallel, one NCCL all-reduce (avg) per parameter issued as its gradient is "
-                      "ready, optimiser applied per parameter as it arrives; backward mode as --backward"}
+                      "n_gpus > 1: data parallel, " + exchange + "; backward mode as --backward"}
