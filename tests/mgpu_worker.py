@@ -1,7 +1,7 @@
 """Worker of tests/test_gpu_multi.py (one process per GPU, launched with torch.distributed.run): trains a small
-L_inf-dist net for a few steps with the copy-engine exchange and with the NCCL all-reduce exchange from the same
-start and data, and checks that (1) both leave the same parameters up to summation order and (2) all replicas of
-the copy-engine run are bit-identical."""
+L_inf-dist net for a few steps with the row-sharded exchanges (NCCL reduce-scatter / all-gather, and copy engines)
+and with the plain all-reduce exchange from the same start and data, and checks that (1) all leave the same
+parameters up to summation order and (2) the replicas of the sharded runs are bit-identical."""
 import os
 import sys
 
@@ -10,13 +10,14 @@ import torch
 import torch.distributed as dist
 
 import linfdist_b200 as L
-from linfdist_b200.train_step import DataParallelStep, MarginLoss, ShardedCopyEngineStep, build_cifar_net, hinge
+from linfdist_b200.train_step import (DataParallelStep, MarginLoss, ShardedCopyEngineStep, ShardedNcclStep,
+                                      build_cifar_net, hinge)
 
 
 def run(kind, dev, rank, steps=3):
     net = build_cifar_net(dev, depth=3, width=1)
     opt = L.AdamW(net, lr=0.02, betas=(0.9, 0.99), eps=1e-10, weight_decay=5e-3)
-    model = (ShardedCopyEngineStep if kind == "copy" else DataParallelStep)(net, opt)
+    model = {"copy": ShardedCopyEngineStep, "sharded": ShardedNcclStep, "nccl": DataParallelStep}[kind](net, opt)
     loss_fn = MarginLoss(hinge(0.75), 1.0)
     gen = torch.Generator().manual_seed(100 + rank)
     for _ in range(steps):
@@ -31,7 +32,7 @@ def run(kind, dev, rank, steps=3):
     torch.cuda.synchronize()
     dist.barrier()
     torch.cuda.synchronize()
-    return [q.detach().clone() for q in net.parameters()], (len(model.big) if kind == "copy" else 0)
+    return [q.detach().clone() for q in net.parameters()], (len(model.big) if kind != "nccl" else 0)
 
 
 def main():
@@ -39,15 +40,16 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
-    a, n_big = run("copy", dev, rank)
     b, _ = run("nccl", dev, rank)
-    assert n_big >= 2, "the large weight matrices must take the copy-engine path"
-    for qa, qb in zip(a, b):
-        torch.testing.assert_close(qa, qb, rtol=1e-5, atol=1e-6)
-    for qa in a:                                   # replicas identical, bit for bit
-        ref = qa.clone()
-        dist.broadcast(ref, src=0)
-        assert torch.equal(ref, qa)
+    for kind in ("copy", "sharded"):
+        a, n_big = run(kind, dev, rank)
+        assert n_big >= 2, "the large weight matrices must take the sharded path"
+        for qa, qb in zip(a, b):
+            torch.testing.assert_close(qa, qb, rtol=1e-5, atol=1e-6)
+        for qa in a:                               # replicas identical, bit for bit
+            ref = qa.clone()
+            dist.broadcast(ref, src=0)
+            assert torch.equal(ref, qa)
     if rank == 0:
         print("MGPU_OK copy-engine exchange on %d ranks, %d sharded tensors" % (dist.get_world_size(), n_big), flush=True)
     dist.barrier()

@@ -9,7 +9,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def test_copy_engine_exchange_matches_allreduce_exchange():
+def test_sharded_exchanges_match_allreduce_exchange():
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     here = os.path.dirname(os.path.abspath(__file__))
