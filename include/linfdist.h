@@ -219,6 +219,24 @@ int linf_adamw_step(float* param, const float* grad, float* exp_avg, float* exp_
                     int rows, int cols, float p_norm, float lr, float beta1, float beta2,
                     float eps, float weight_decay, int step, void* stream);
 
+/*
+ * Host-side helpers of the copy-engine gradient exchange of the data-parallel training step
+ * (ShardedCopyEngineStep in the Python package).  No counterpart in the reference, whose data
+ * parallelism is torch's DistributedDataParallel over NCCL (main.py:195-199).
+ *
+ * linf_peer_push: queues n_copies asynchronous copies dst[i] <- src[i] of bytes[i] bytes on
+ * `stream` (device memory of this GPU or memory of a peer mapped into this process; the copies run
+ * on the copy engines, no kernel is launched), then n_flags writes of flag_value to the 32-bit words
+ * flag_addr[i] (4-byte aligned, typically in the receivers' memory) as ONE batched stream memory
+ * operation ordered behind the copies.  n_flags <= 64.
+ * linf_flags_wait: makes `stream` wait, without a kernel, until every 32-bit word flag_addr[i] has
+ * reached `value` (cyclic comparison (int)(*addr - value) >= 0).  The wait has no time limit: a
+ * peer that never writes leaves the stream waiting, like a collective whose peer died.
+ */
+int linf_peer_push(int n_copies, void* const* dst, const void* const* src, const size_t* bytes,
+                   int n_flags, void* const* flag_addr, unsigned int flag_value, void* stream);
+int linf_flags_wait(int n_flags, void* const* flag_addr, unsigned int value, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -6,7 +6,7 @@ import subprocess
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "liblinfdist.so")
 CSRC = os.path.join(_HERE, "csrc")
-SOURCES = ["adamw.cu", "api.cu", "inf_forward.cu", "inf_bound.cu", "inf_backward.cu", "inf_backward_accum.cu", "lp.cu", "lp_tiled.cu", "no_alloc.cu", "skinny.cu"]
+SOURCES = ["adamw.cu", "api.cu", "inf_forward.cu", "inf_bound.cu", "inf_backward.cu", "inf_backward_accum.cu", "lp.cu", "lp_tiled.cu", "no_alloc.cu", "peer_push.cu", "skinny.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "--shared", "-Xcompiler", "-fPIC"]
 
@@ -29,6 +29,8 @@ _PROTOS = {
     "linf_inf_dist_backward_atomic": [_F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F, _F],
     "linf_adamw_step": [_F, _F, _F, _F, _INT, _INT, ctypes.c_float, ctypes.c_float, ctypes.c_float, ctypes.c_float,
                         ctypes.c_float, ctypes.c_float, _INT, _F],
+    "linf_peer_push": [_INT, _F, _F, _F, _INT, _F, ctypes.c_uint, _F],
+    "linf_flags_wait": [_INT, _F, ctypes.c_uint, _F],
     "linf_norm_dist_forward": [_F, _F, _INT, _INT, _INT, _INT, _INT, _F, ctypes.c_float, _F],
     "linf_norm_dist_backward_input": [_F, _F, _F, _F, _INT, _INT, _INT, _INT, _INT, _F, ctypes.c_float, _F],
     "linf_norm_dist_backward_weight": [_F, _F, _F, _F, _INT, _INT, _INT, _INT, _INT, _F, ctypes.c_float, _F],

@@ -8,6 +8,7 @@ import math
 import torch
 import torch.nn as nn
 
+from . import _lib
 from .adamw import AdamW
 from .bound_module import BoundFinalIdentity, Predictor
 from .nets import MLP, MLPFeature, Model
@@ -245,12 +246,12 @@ class ShardedCopyEngineStep(DataParallelStep):
 
     def __init__(self, net, optimizer):
         import torch.distributed as dist
+        import ctypes
         import torch.distributed._symmetric_memory as symm_mem
-        from cuda.bindings import driver as cu
         super().__init__(net, optimizer)
         if not (self.cuda and self.world > 1):
             raise RuntimeError("ShardedCopyEngineStep needs CUDA tensors and more than one rank")
-        self.cu = cu
+        self.lib = _lib.load()
         self.rank = dist.get_rank()
         self.copy = torch.cuda.Stream()      # gradient chunks to their owners
         self.push = torch.cuda.Stream()      # updated rows to every replica
@@ -277,53 +278,29 @@ class ShardedCopyEngineStep(DataParallelStep):
                 "peer_flags": [hf.get_buffer(j, (2 * W,), torch.int32) for j in range(W)],
                 "reduced": torch.empty(s, cols, dtype=torch.float32, device=p.device),
                 "updated": torch.cuda.Event(), "pushed": torch.cuda.Event(),
-                "c_fwd": {}, "c_rs": {}, "c_wait": {}, "c_ag": {},
             }
+            b = self.big[id(p)]
+            chunk = s * cols * 4
+            b["chunk_bytes"] = chunk
+            b["bytes"] = (ctypes.c_size_t * (W - 1))(*([chunk] * (W - 1)))
+            # gradient chunk r lands in slot r of the owner's staging area; its flag is word r there
+            b["d_rs"] = self._ptrs([b["peer_stage"][j][r].data_ptr() for j in b["others"]])
+            b["f_rs"] = self._ptrs([b["peer_flags"][j].data_ptr() + 4 * r for j in b["others"]])
+            b["f_wait"] = self._ptrs([flags.data_ptr() + 4 * j for j in b["others"]])
+            # updated rows of this rank into every replica; flag word W + r there
+            b["s_ag"] = self._ptrs([b["store"][r * s:(r + 1) * s].data_ptr()] * (W - 1))
+            b["d_ag"] = self._ptrs([b["peer_store"][j][r * s:(r + 1) * s].data_ptr() for j in b["others"]])
+            b["f_ag"] = self._ptrs([b["peer_flags"][j].data_ptr() + 4 * (W + r) for j in b["others"]])
+            b["f_fwd"] = self._ptrs([flags.data_ptr() + 4 * (W + j) for j in b["others"]])
         torch.cuda.synchronize()
         dist.barrier()
 
-    # ---- stream memory operations and peer copies through the driver API (no kernel, no SM; one
-    # driver call per group of flags keeps the host cost of a step low) ----
-    def _flag_ops(self, stream, wait, tensors_indices, value, cache=None):
-        """One driver call that waits for (wait=True) or writes `value` at the given flag words.  The
-        array of operations of a call site is built once (`cache`: a dict entry of the caller) and only
-        its values change from step to step."""
-        cu = self.cu
-        ops = cache.get("ops") if cache is not None else None
-        if ops is None:
-            ops = []
-            for tensor, index in tensors_indices:
-                op = cu.CUstreamBatchMemOpParams()
-                if wait:
-                    op.operation = cu.CUstreamBatchMemOpType.CU_STREAM_MEM_OP_WAIT_VALUE_32
-                    op.waitValue.operation = cu.CUstreamBatchMemOpType.CU_STREAM_MEM_OP_WAIT_VALUE_32
-                    op.waitValue.address = tensor.data_ptr() + 4 * index
-                    op.waitValue.flags = int(cu.CUstreamWaitValue_flags.CU_STREAM_WAIT_VALUE_GEQ)
-                else:
-                    op.operation = cu.CUstreamBatchMemOpType.CU_STREAM_MEM_OP_WRITE_VALUE_32
-                    op.writeValue.operation = cu.CUstreamBatchMemOpType.CU_STREAM_MEM_OP_WRITE_VALUE_32
-                    op.writeValue.address = tensor.data_ptr() + 4 * index
-                    op.writeValue.flags = 0
-                ops.append(op)
-            if cache is not None:
-                cache["ops"] = ops
-                cache["stream"] = cu.CUstream(stream.cuda_stream)
-        for op in ops:
-            if wait:
-                op.waitValue.value = value
-            else:
-                op.writeValue.value = value
-        handle = cache["stream"] if cache is not None else cu.CUstream(stream.cuda_stream)
-        rc = cu.cuStreamBatchMemOp(handle, len(ops), ops, 0)
-        if rc[0] != cu.CUresult.CUDA_SUCCESS:
-            raise RuntimeError("cuStreamBatchMemOp: %s" % (rc[0],))
-
-    def _push(self, stream, dst, src):
-        """Asynchronous copy of `src` (local) into `dst` (a view of a peer's symmetric memory)."""
-        rc = self.cu.cuMemcpyAsync(self.cu.CUdeviceptr(dst.data_ptr()), self.cu.CUdeviceptr(src.data_ptr()),
-                                   src.numel() * src.element_size(), self.cu.CUstream(stream.cuda_stream))
-        if rc[0] != self.cu.CUresult.CUDA_SUCCESS:
-            raise RuntimeError("cuMemcpyAsync: %s" % (rc[0],))
+    # ---- grouped peer copies and flag operations: one call into the library per group (no kernel,
+    # no SM; csrc/peer_push.cu) ----
+    @staticmethod
+    def _ptrs(values):
+        import ctypes
+        return (ctypes.c_void_p * len(values))(*values)
 
     def _make_wait(self, own):
         base = super()._make_wait(own)
@@ -335,7 +312,7 @@ class ShardedCopyEngineStep(DataParallelStep):
                 b = self.big.get(id(q))
                 if b is not None and b["step"] > 0:
                     cur.wait_event(b["updated"])
-                    self._flag_ops(cur, True, [(b["flags"], self.world + j) for j in b["others"]], b["step"], b["c_fwd"])
+                    _lib.check(self.lib.linf_flags_wait(self.world - 1, b["f_fwd"], b["step"], cur.cuda_stream), "flags_wait")
         return wait
 
     def _issue(self, p):
@@ -343,6 +320,7 @@ class ShardedCopyEngineStep(DataParallelStep):
         if b is None:
             return super()._issue(p)
         W, r, s, cols = self.world, self.rank, b["s"], b["cols"]
+        n = W - 1
         b["step"] += 1
         t = b["step"]
         grad = p.grad.view(W, s * cols)
@@ -352,16 +330,16 @@ class ShardedCopyEngineStep(DataParallelStep):
         p.grad.record_stream(self.side)
         # 1. chunks of this rank's gradient to their owners, then the "chunk from r has landed" flags
         self.copy.wait_event(ready)
-        for j in b["others"]:                     # starts with the right-hand neighbour: spreads the load
-            self._push(self.copy, b["peer_stage"][j][r], grad[j])
-        self._flag_ops(self.copy, False, [(b["peer_flags"][j], r) for j in b["others"]], t, b["c_rs"])
+        g0 = p.grad.data_ptr()
+        src = self._ptrs([g0 + j * b["chunk_bytes"] for j in b["others"]])
+        _lib.check(self.lib.linf_peer_push(n, b["d_rs"], src, b["bytes"], n, b["f_rs"], t, self.copy.cuda_stream), "peer_push")
         # 2. own shard: wait for the W-1 chunks, add in rank order, average, update the rows
         with torch.cuda.stream(self.side):
             self.side.wait_event(ready)
             if t > 1:
                 self.side.wait_event(b["pushed"])     # last step's pushes have read the rows about to change
             b["stage"][r].copy_(grad[r], non_blocking=True)
-            self._flag_ops(self.side, True, [(b["flags"], j) for j in b["others"]], t, b["c_wait"])
+            _lib.check(self.lib.linf_flags_wait(n, b["f_wait"], t, self.side.cuda_stream), "flags_wait")
             torch.sum(b["stage"].view(W, s, cols), dim=0, out=b["reduced"])
             b["reduced"].mul_(1.0 / W)
             self.opt.step_rows(p, r * s, s, b["reduced"])
@@ -369,10 +347,7 @@ class ShardedCopyEngineStep(DataParallelStep):
         # 3. the updated rows to every replica, on a stream of their own so that the next
         #    parameter's reduction does not queue behind these copies
         self.push.wait_event(b["updated"])
-        mine = b["store"][r * s:(r + 1) * s]
-        for j in b["others"]:
-            self._push(self.push, b["peer_store"][j][r * s:(r + 1) * s], mine)
-        self._flag_ops(self.push, False, [(b["peer_flags"][j], W + r) for j in b["others"]], t, b["c_ag"])
+        _lib.check(self.lib.linf_peer_push(n, b["d_ag"], b["s_ag"], b["bytes"], n, b["f_ag"], t, self.push.cuda_stream), "peer_push")
         b["pushed"].record(self.push)
 
     def synchronize(self):
