@@ -512,3 +512,52 @@ def test_inf_forward_tma_loader_variant(cuda, lib, shape):
         assert lib.linf_tune_set(2, 0) == 0
     finally:
         lib.linf_tune_set(0, 2)
+
+
+def test_adamw_step_rows_equals_whole_tensor_step(cuda, lib):
+    """Updating a weight matrix in row blocks, each block with moments of its own (what the sharded
+    data-parallel steps do on every rank), leaves exactly the bits of one update of the whole matrix."""
+    import linfdist_b200 as L
+
+    def make():
+        torch.manual_seed(5)
+        m = L.NormDist(256, 64, bias=False).cuda()
+        m.weight.data = torch.randn(64, 256, 1, 1, device="cuda")
+        return m
+
+    whole, parts = make(), make()
+    ow = L.AdamW(whole, lr=0.02, betas=(0.9, 0.99), eps=1e-10, weight_decay=5e-3)
+    op = L.AdamW(parts, lr=0.02, betas=(0.9, 0.99), eps=1e-10, weight_decay=5e-3)
+    gen = torch.Generator(device="cuda").manual_seed(2)
+    for _ in range(3):
+        g = torch.randn(64, 256, 1, 1, device="cuda", generator=gen)
+        whole.weight.grad = g.clone()
+        ow.step()
+        for r0 in range(0, 64, 16):
+            op.step_rows(parts.weight, r0, 16, g.view(64, 256)[r0:r0 + 16].contiguous())
+    torch.cuda.synchronize()
+    assert torch.equal(whole.weight.data, parts.weight.data)
+
+
+def test_peer_push_and_flags_on_one_gpu(cuda, lib):
+    """The grouped copy + flag helpers of the copy-engine exchange, exercised inside one GPU: copies
+    land, flags are written behind them, and a wait on flags that already hold the value returns."""
+    import ctypes
+    src = torch.arange(3 * 1000, dtype=torch.float32, device="cuda").view(3, 1000)
+    dst = torch.zeros(3, 1000, device="cuda")
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    ptrs = lambda v: (ctypes.c_void_p * len(v))(*v)
+    s = torch.cuda.Stream()
+    rc = lib.linf_peer_push(3, ptrs([dst[i].data_ptr() for i in range(3)]), ptrs([src[i].data_ptr() for i in range(3)]),
+                            (ctypes.c_size_t * 3)(4000, 4000, 4000), 2, ptrs([flags.data_ptr() + 4, flags.data_ptr() + 20]),
+                            7, s.cuda_stream)
+    assert rc == 0
+    s.synchronize()
+    assert torch.equal(dst, src) and flags.tolist() == [0, 7, 0, 0, 0, 7, 0, 0]
+    # only now, with the value known to be there, queue a wait for it (and for an older value)
+    assert lib.linf_flags_wait(2, ptrs([flags.data_ptr() + 4, flags.data_ptr() + 20]), 7, s.cuda_stream) == 0
+    assert lib.linf_flags_wait(1, ptrs([flags.data_ptr() + 4]), 3, s.cuda_stream) == 0
+    s.synchronize()
+    assert lib.linf_peer_push(0, None, None, None, 65, ptrs([flags.data_ptr()] * 65), 1, s.cuda_stream) == 2   # too many flags
+    assert lib.linf_flags_wait(1, ptrs([flags.data_ptr() + 2]), 1, s.cuda_stream) == 6                          # misaligned word
