@@ -14,9 +14,10 @@
 //      and the finished row is written out whole (no zero fill of the destination needed).
 // Every bin therefore sees sequential fp32 adds in ascending source order: a fixed,
 // reproducible order, and one of the orders the reference's atomicAdd scatter can produce.
-// Two implementations: inf_backward_rows_kernel keeps the row's sources in registers (rows that
-// fit their thread group: the dense-layer shapes); inf_backward_ordered_kernel is the general
-// one (any row length, sparse rows through a bitmap of occurring bins, conv-shaped tensors).
+// Implementations: inf_backward_rows_kernel keeps the row's sources in registers (grad_input rows
+// of up to 12288 sources); inf_backward_ordered_kernel is the general one (any row length, sparse
+// rows through a bitmap of occurring bins, conv-shaped tensors).  Dense grad_weight rows do not
+// sort at all: inf_backward_accum.cu.
 //
 // Atomic kernel: one pass over (grad_output, pos) produces both gradients with fp32 atomics;
 // for grad_weight a 32 x 32 tile is transposed through shared memory so that the lanes of a
@@ -284,54 +285,43 @@ inf_backward_ordered_kernel(const float* __restrict__ gout, const int* __restric
 }
 
 // --------------------------------------------------------------------------------------------
-// Fast ordered path: same four steps, but every thread keeps its share of the row's sources
-// (EPT of them) in registers from the first load to the placement, slots inside a bin come
-// from one shared-memory atomic per source, and step 4 restores ascending source order with
-// an insertion sort on the source indices that travel with the values (only sources that were
-// in flight at the same time can be out of order, so the sort is close to a no-op).
-//   CTA_ROW = true : one CTA (256 threads) per row, sources read straight from global memory
-//   CTA_ROW = false: one warp per row, 8 neighbouring rows per CTA; the CTA first copies the
-//                    sources of its rows into shared memory (rows of grad_weight read with a
-//                    stride of CO floats; neighbouring rows share each 32-byte sector)
+// Fast ordered path for grad_input rows: same four steps, but every thread keeps its share of the
+// row's sources (EPT of them) in registers from the first load to the placement, slots inside a
+// bin come from one shared-memory atomic per source, and step 4 restores ascending source order
+// with an insertion sort on the source indices that travel with the values (only sources that
+// were in flight at the same time can be out of order, so the sort is close to a no-op).
+// One CTA of 16 warps per row, sources read straight from global memory.
 // --------------------------------------------------------------------------------------------
-// C = number of copies of the count array (CTA rows only): warps of different copies place in parallel
+// C = number of copies of the count array: warps of different copies place in parallel
 __host__ __device__ inline int fast_copies(int nb) {
     int c = 1;
     while (c < 8 && (2 * c - 1) * (nb + 1) * 4 <= 16 * 1024) c <<= 1;
     return c;
 }
-__host__ __device__ inline int fast_group_words(int nb, int n_src, bool staged) {
-    const int a = staged ? max(2 * n_src, 2 * nb + 2) : (fast_copies(nb) + 1) * (nb + 1);   // staged copy aliases hist + seg
-    return a + 32 + n_src + (n_src + 1) / 2;
+__host__ __device__ inline int fast_group_words(int nb, int n_src) {
+    return (fast_copies(nb) + 1) * (nb + 1) + 32 + n_src + (n_src + 1) / 2;
 }
 
-template <int MODE, bool CTA_ROW, int EPT>
-__global__ void __launch_bounds__(CTA_ROW ? 512 : 256)
+template <int MODE, int EPT>
+__global__ void __launch_bounds__(512)
 inf_backward_rows_kernel(const float* __restrict__ gout, const int* __restrict__ pos, Dims d,
                          float* __restrict__ dst, int n_rows, int n_src) {
     extern __shared__ __align__(16) int smem_i[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int GS = CTA_ROW ? blockDim.x : 32;
-    const int gt = CTA_ROW ? threadIdx.x : lane;
-    const int gwp = CTA_ROW ? warp : 0;
-    const int rpc = CTA_ROW ? 1 : (blockDim.x >> 5);
-    const int row0 = blockIdx.x * rpc;
-    const int row = row0 + (CTA_ROW ? 0 : warp);
+    const int GS = blockDim.x, gt = threadIdx.x;
+    const int row = blockIdx.x;
     const int nb = d.CIg, HW = d.HW;
-    const int gwords = fast_group_words(nb, n_src, !CTA_ROW);
-    int* base = smem_i + (CTA_ROW ? 0 : (size_t)warp * gwords);
-    const int C = CTA_ROW ? fast_copies(nb) : 1;         // copies of the count / cursor array
-    const int WPC = CTA_ROW ? max(1, (int)(blockDim.x >> 5) / C) : 1;   // warps that share a copy
-    int* hist = base;                                    // [C][nb + 1] counts, then cursors
+    const int C = fast_copies(nb);                       // copies of the count / cursor array
+    const int WPC = max(1, (int)(blockDim.x >> 5) / C);  // warps that share a copy
+    int* hist = smem_i;                                  // [C][nb + 1] counts, then cursors
     int* seg = hist + C * (nb + 1);                      // [nb + 1] first slot of every bin
-    const int a_words = CTA_ROW ? (C + 1) * (nb + 1) : max(2 * n_src, 2 * nb + 2);
-    int* myhist = hist + (CTA_ROW ? (gwp / WPC) * (nb + 1) : 0);
-    int* wsum = base + a_words;                          // [32]: warp sums of the scan; [24] = work-list length
+    int* myhist = hist + (warp / WPC) * (nb + 1);
+    int* wsum = smem_i + (C + 1) * (nb + 1);             // [32]: warp sums of the scan; [24] = work-list length
     float* sorted = reinterpret_cast<float*>(wsum + 32); // [n_src]
     unsigned short* skey = reinterpret_cast<unsigned short*>(sorted + n_src);   // [n_src] source index of a slot
 
     int pv[EPT]; float gv[EPT];
-    if (CTA_ROW) {
+    {
         size_t s_base; int s_step;
         if (MODE == 0) {
             const int r = row / d.G, g = row - r * d.G, b = r / HW, hw = r - b * HW;
@@ -342,7 +332,7 @@ inf_backward_rows_kernel(const float* __restrict__ gout, const int* __restrict__
         }
 #pragma unroll
         for (int j = 0; j < EPT; ++j) {
-            const int e = (gwp * EPT + j) * 32 + lane;   // warp w owns sources [w*EPT*32, (w+1)*EPT*32)
+            const int e = (warp * EPT + j) * 32 + lane;  // warp w owns sources [w*EPT*32, (w+1)*EPT*32)
             pv[j] = -1; gv[j] = 0.f;
             if (e < n_src) {
                 size_t a;
@@ -351,48 +341,7 @@ inf_backward_rows_kernel(const float* __restrict__ gout, const int* __restrict__
                 pv[j] = __ldg(pos + a); gv[j] = __ldg(gout + a);
             }
         }
-    } else {
-        // stage: consecutive threads read consecutive rows (channels) of one source
-        const int total = rpc * n_src;
-        auto stage_addr = [&](int q, int& j, int& e) -> size_t {
-            j = q % rpc; e = q / rpc;
-            const int rowj = min(row0 + j, n_rows - 1);
-            if (MODE == 0) {
-                const int r = rowj / d.G, g = rowj - r * d.G, b = r / HW, hw = r - b * HW;
-                return ((size_t)(b * d.G + g) * d.COg + e) * HW + hw;
-            }
-            const int g = rowj / d.COg, o = rowj - g * d.COg, b = e / HW, hw = e - b * HW;
-            return ((size_t)(b * d.G + g) * d.COg + o) * HW + hw;
-        };
-        constexpr int SU = 8;                            // loads in flight per thread
-        for (int q0 = threadIdx.x; q0 < total; q0 += SU * blockDim.x) {
-            int pj[SU], pe[SU], pp[SU]; float pg[SU];
-#pragma unroll
-            for (int u = 0; u < SU; ++u) {
-                const int q = q0 + u * blockDim.x;
-                pp[u] = -1; pg[u] = 0.f; pj[u] = 0; pe[u] = 0;
-                if (q < total) { const size_t a = stage_addr(q, pj[u], pe[u]); pp[u] = __ldg(pos + a); pg[u] = __ldg(gout + a); }
-            }
-#pragma unroll
-            for (int u = 0; u < SU; ++u) {
-                if (q0 + u * blockDim.x < total) {
-                    int* sp = smem_i + (size_t)pj[u] * gwords;
-                    sp[pe[u]] = pp[u];
-                    reinterpret_cast<float*>(sp + n_src)[pe[u]] = pg[u];
-                }
-            }
-        }
-        __syncthreads();
-        if (row >= n_rows) return;
-#pragma unroll
-        for (int j = 0; j < EPT; ++j) {
-            const int e = j * 32 + lane;
-            pv[j] = e < n_src ? base[e] : -1;
-            gv[j] = e < n_src ? reinterpret_cast<float*>(base + n_src)[e] : 0.f;
-        }
-        __syncwarp();                                    // the staged copy is dead: reuse it as hist/seg
     }
-    auto sync = [&]() { if (CTA_ROW) __syncthreads(); else __syncwarp(); };
 
     size_t d_base; int d_step;
     if (MODE == 0) {
@@ -404,13 +353,13 @@ inf_backward_rows_kernel(const float* __restrict__ gout, const int* __restrict__
 
     // ---- 1. histogram ----
     for (int i = gt; i < C * (nb + 1); i += GS) hist[i] = 0;
-    sync();
+    __syncthreads();
 #pragma unroll
     for (int j = 0; j < EPT; ++j) {
         const int idx = pv[j] & 0x7fffffff;
         if (idx < nb) atomicAdd(&myhist[idx], 1);        // an index outside the group is dropped
     }
-    sync();
+    __syncthreads();
     // ---- 2. first slot of every bin (and of every copy's share of the bin) ----
     if (C > 1) {
         for (int i = gt; i < nb; i += GS) {
@@ -418,129 +367,79 @@ inf_backward_rows_kernel(const float* __restrict__ gout, const int* __restrict__
             for (int c = 0; c < C; ++c) { const int t = hist[c * (nb + 1) + i]; hist[c * (nb + 1) + i] = run; run += t; }
             seg[i] = run;
         }
-        sync();
-        group_exclusive_scan<CTA_ROW>(seg, nb, gt, GS, lane, gwp, wsum);
+        __syncthreads();
+        group_exclusive_scan<true>(seg, nb, gt, GS, lane, warp, wsum);
         for (int c = 0; c < C; ++c)
             for (int i = gt; i < nb; i += GS) hist[c * (nb + 1) + i] += seg[i];
     } else {
-        group_exclusive_scan<CTA_ROW>(hist, nb, gt, GS, lane, gwp, wsum);
+        group_exclusive_scan<true>(hist, nb, gt, GS, lane, warp, wsum);
         for (int i = gt; i <= nb; i += GS) seg[i] = hist[i];
     }
-    sync();
+    __syncthreads();
     // ---- 3. placement: value and source index into the next free slot of the bin ----
+    // The warps own ascending source ranges.  Warps that share a copy of the cursor array take
+    // their slots one warp after the other, each warp in ascending batches; warps of different
+    // copies own disjoint slot ranges of a bin and run in parallel.  A bin then fills in
+    // ascending source order provided the lanes of one atomic instruction are served in lane
+    // order.  That last point is hardware behaviour, not a guarantee, so the source index
+    // travels along and step 4 checks it.
+    for (int w = 0; w < WPC; ++w) {
+        if (warp % WPC == w) {
+            int slot[EPT];
 #pragma unroll
-    for (int j = 0; j < EPT; ++j) {
-        const int idx = pv[j] & 0x7fffffff;
-        float val = (pv[j] >= 0) ? gv[j] : -gv[j];
-        if (MODE == 1) val = -val;
-        if (CTA_ROW) {
-            // done further down, one warp after the other
-        } else {
-            // one warp owns the row and walks it 32 sources at a time: lanes that share a bin take
-            // consecutive slots in lane order, so the bin is filled in ascending source order
-            const bool active = idx < nb;
-            const unsigned act = __ballot_sync(FULL, active);
-            int rank = 0, leader = lane, cur = 0;
-            if (active) {
-                const unsigned grp = __match_any_sync(act, idx);
-                rank = __popc(grp & ((1u << lane) - 1u));
-                leader = __ffs(grp) - 1;
-                if (rank == 0) { cur = myhist[idx]; myhist[idx] = cur + __popc(grp); }
+            for (int j = 0; j < EPT; ++j) {
+                const int idx = pv[j] & 0x7fffffff;
+                slot[j] = idx < nb ? atomicAdd(&myhist[idx], 1) : -1;
             }
-            cur = __shfl_sync(FULL, cur, leader);
-            if (active) sorted[cur + rank] = val;
-            __syncwarp();
-        }
-    }
-    if (CTA_ROW) {
-        // The warps own ascending source ranges.  Warps that share a copy of the cursor array take
-        // their slots one warp after the other, each warp in ascending batches; warps of different
-        // copies own disjoint slot ranges of a bin and run in parallel.  A bin then fills in
-        // ascending source order provided the lanes of one atomic instruction are served in lane
-        // order.  That last point is hardware behaviour, not a guarantee, so the source index
-        // travels along and step 4 checks it.
-        for (int w = 0; w < WPC; ++w) {
-            if (gwp % WPC == w) {
-                int slot[EPT];
 #pragma unroll
-                for (int j = 0; j < EPT; ++j) {
-                    const int idx = pv[j] & 0x7fffffff;
-                    slot[j] = idx < nb ? atomicAdd(&myhist[idx], 1) : -1;
-                }
-#pragma unroll
-                for (int j = 0; j < EPT; ++j) {
-                    if (slot[j] >= 0) {
-                        float val = (pv[j] >= 0) ? gv[j] : -gv[j];
-                        if (MODE == 1) val = -val;
-                        sorted[slot[j]] = val;
-                        skey[slot[j]] = (unsigned short)((gwp * EPT + j) * 32 + lane);
-                    }
+            for (int j = 0; j < EPT; ++j) {
+                if (slot[j] >= 0) {
+                    float val = (pv[j] >= 0) ? gv[j] : -gv[j];
+                    if (MODE == 1) val = -val;
+                    sorted[slot[j]] = val;
+                    skey[slot[j]] = (unsigned short)((warp * EPT + j) * 32 + lane);
                 }
             }
-            __syncthreads();
         }
+        __syncthreads();
     }
-    sync();
     // ---- 4. per bin: ascending source order, then sequential fp32 adds from +0 ----
-    if (CTA_ROW) {
-        // First pass: one thread per bin adds in slot order while checking that the source indices
-        // ascend; a bin that fails the check goes on a work list (kept in the cursor array, which
-        // is dead now).  Second pass: the listed bins are sorted by source index and added again.
-        if (gt == 0) wsum[24] = 0;
-        __syncthreads();
-        for (int i = gt; i < nb; i += GS) {
-            const int s0 = seg[i], s1 = seg[i + 1];
-            float acc = 0.f;
-            bool ordered = true;
-            int prev = -1, j = s0;
-            for (; j + 2 <= s1; j += 2) {
-                const int k0 = skey[j], k1 = skey[j + 1];
-                const float v0 = sorted[j], v1 = sorted[j + 1];
-                ordered = ordered && (k0 > prev) && (k1 > k0);
-                prev = k1;
-                acc += v0; acc += v1;
-            }
-            if (j < s1) { ordered = ordered && ((int)skey[j] > prev); acc += sorted[j]; }
-            if (ordered) dst[d_base + (size_t)i * d_step] = acc;
-            else hist[atomicAdd(&wsum[24], 1)] = i;
+    // First pass: one thread per bin adds in slot order while checking that the source indices
+    // ascend; a bin that fails the check goes on a work list (kept in the cursor array, which
+    // is dead now).  Second pass: the listed bins are sorted by source index and added again.
+    if (gt == 0) wsum[24] = 0;
+    __syncthreads();
+    for (int i = gt; i < nb; i += GS) {
+        const int s0 = seg[i], s1 = seg[i + 1];
+        float acc = 0.f;
+        bool ordered = true;
+        int prev = -1, j = s0;
+        for (; j + 2 <= s1; j += 2) {
+            const int k0 = skey[j], k1 = skey[j + 1];
+            const float v0 = sorted[j], v1 = sorted[j + 1];
+            ordered = ordered && (k0 > prev) && (k1 > k0);
+            prev = k1;
+            acc += v0; acc += v1;
         }
-        __syncthreads();
-        const int n_list = wsum[24];
-        for (int q = gt; q < n_list; q += GS) {
-            const int i = hist[q];
-            const int s0 = seg[i], s1 = seg[i + 1];
-            for (int a = s0 + 1; a < s1; ++a) {
-                const unsigned short k = skey[a];
-                const float v = sorted[a];
-                int b2 = a - 1;
-                while (b2 >= s0 && skey[b2] > k) { skey[b2 + 1] = skey[b2]; sorted[b2 + 1] = sorted[b2]; --b2; }
-                skey[b2 + 1] = k; sorted[b2 + 1] = v;
-            }
-            float acc = 0.f;
-            for (int a = s0; a < s1; ++a) acc += sorted[a];
-            dst[d_base + (size_t)i * d_step] = acc;
+        if (j < s1) { ordered = ordered && ((int)skey[j] > prev); acc += sorted[j]; }
+        if (ordered) dst[d_base + (size_t)i * d_step] = acc;
+        else hist[atomicAdd(&wsum[24], 1)] = i;
+    }
+    __syncthreads();
+    const int n_list = wsum[24];
+    for (int q = gt; q < n_list; q += GS) {
+        const int i = hist[q];
+        const int s0 = seg[i], s1 = seg[i + 1];
+        for (int a = s0 + 1; a < s1; ++a) {
+            const unsigned short k = skey[a];
+            const float v = sorted[a];
+            int b2 = a - 1;
+            while (b2 >= s0 && skey[b2] > k) { skey[b2 + 1] = skey[b2]; sorted[b2 + 1] = sorted[b2]; --b2; }
+            skey[b2 + 1] = k; sorted[b2 + 1] = v;
         }
-    } else {
-        for (int i = gt; i < nb; i += GS) {
-            const int s0 = seg[i], s1 = seg[i + 1];
-            float acc = 0.f;
-            int j = s0;
-            // long bins (one bin often collects most of a weight row's sources): keep 16 loads in
-            // flight ahead of the dependent chain of adds
-            for (; j + 16 <= s1; j += 16) {
-                float v[16];
-#pragma unroll
-                for (int q = 0; q < 16; ++q) v[q] = sorted[j + q];
-#pragma unroll
-                for (int q = 0; q < 16; ++q) acc += v[q];
-            }
-            for (; j + 4 <= s1; j += 4) {
-                const float v0 = sorted[j], v1 = sorted[j + 1], v2 = sorted[j + 2], v3 = sorted[j + 3];
-                acc += v0; acc += v1; acc += v2; acc += v3;
-            }
-            for (; j < s1; ++j) acc += sorted[j];
-            dst[d_base + (size_t)i * d_step] = acc;
-        }
+        float acc = 0.f;
+        for (int a = s0; a < s1; ++a) acc += sorted[a];
+        dst[d_base + (size_t)i * d_step] = acc;
     }
 }
 
@@ -613,15 +512,14 @@ int launch_ordered_as(const float* g, const int* pos, const Dims& d, float* dst,
     return launch_status();
 }
 
-template <int MODE, bool CTA_ROW, int EPT>
+template <int MODE, int EPT>
 int launch_fast(const float* g, const int* pos, const Dims& d, float* dst, cudaStream_t st,
                 int n_rows, int n_src, int warps, size_t smem) {
-    auto kern = inf_backward_rows_kernel<MODE, CTA_ROW, EPT>;
+    auto kern = inf_backward_rows_kernel<MODE, EPT>;
     if (smem > 40 * 1024 &&
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT) != cudaSuccess)
         return LINF_ERR_LAUNCH;
-    const int grid = CTA_ROW ? n_rows : (n_rows + warps - 1) / warps;
-    kern<<<grid, 32 * warps, smem, st>>>(g, pos, d, dst, n_rows, n_src);
+    kern<<<n_rows, 32 * warps, smem, st>>>(g, pos, d, dst, n_rows, n_src);
     return launch_status();
 }
 
@@ -636,29 +534,18 @@ int launch_ordered(const float* g, const int* pos, const Dims& d, float* dst, cu
         if (rc >= 0) return rc;
     }
     {
-        // fast path (sources held in registers) whenever the row fits its thread group
+        // grad_input: fast path (sources held in registers) whenever the row fits its thread group
+        // (dense grad_weight rows were taken by the sort-free kernel above)
         int rc = -1;
-        if (MODE == 1 && d.HW == 1 && n_src <= 512 && nb <= 2 * n_src) {
-            const size_t gb = (size_t)fast_group_words(nb, n_src, true) * 4;
-            int rpc = (int)(SMEM_LIMIT / gb);
-            if (rpc > 8) rpc = 8;
-            if (rpc >= 1) {
-                // keep at least two CTAs per SM when eight rows would take more than half of it
-                while (rpc & (rpc - 1)) --rpc;                       // power of two
-                while (rpc > 2 && gb * rpc > 100 * 1024) rpc >>= 1;
-                if (n_src <= 128) rc = launch_fast<MODE, false, 4>(g, pos, d, dst, st, n_rows, n_src, rpc, gb * rpc);
-                else if (n_src <= 256) rc = launch_fast<MODE, false, 8>(g, pos, d, dst, st, n_rows, n_src, rpc, gb * rpc);
-                else rc = launch_fast<MODE, false, 16>(g, pos, d, dst, st, n_rows, n_src, rpc, gb * rpc);
-            }
-        } else if (MODE == 0 && n_src <= 512 * 24) {
+        if (MODE == 0 && n_src <= 512 * 24) {
             // one CTA of 16 warps per row; the smallest per-thread share that covers the row
-            const size_t gb = (size_t)fast_group_words(nb, n_src, false) * 4;
+            const size_t gb = (size_t)fast_group_words(nb, n_src) * 4;
             if (gb <= SMEM_LIMIT) {
-                if (n_src <= 512 * 4) rc = launch_fast<MODE, true, 4>(g, pos, d, dst, st, n_rows, n_src, 16, gb);
-                else if (n_src <= 512 * 8) rc = launch_fast<MODE, true, 8>(g, pos, d, dst, st, n_rows, n_src, 16, gb);
-                else if (n_src <= 512 * 12) rc = launch_fast<MODE, true, 12>(g, pos, d, dst, st, n_rows, n_src, 16, gb);
-                else if (n_src <= 512 * 16) rc = launch_fast<MODE, true, 16>(g, pos, d, dst, st, n_rows, n_src, 16, gb);
-                else rc = launch_fast<MODE, true, 24>(g, pos, d, dst, st, n_rows, n_src, 16, gb);
+                if (n_src <= 512 * 4) rc = launch_fast<MODE, 4>(g, pos, d, dst, st, n_rows, n_src, 16, gb);
+                else if (n_src <= 512 * 8) rc = launch_fast<MODE, 8>(g, pos, d, dst, st, n_rows, n_src, 16, gb);
+                else if (n_src <= 512 * 12) rc = launch_fast<MODE, 12>(g, pos, d, dst, st, n_rows, n_src, 16, gb);
+                else if (n_src <= 512 * 16) rc = launch_fast<MODE, 16>(g, pos, d, dst, st, n_rows, n_src, 16, gb);
+                else rc = launch_fast<MODE, 24>(g, pos, d, dst, st, n_rows, n_src, 16, gb);
             }
         }
         if (rc >= 0) return rc;
