@@ -81,6 +81,12 @@ __device__ __forceinline__ void add_batch(float* __restrict__ acc, const Batch& 
     __syncwarp();
 }
 
+// COMPACT (rows much longer than their number of sources, all sources in one staged block): the
+// warp does not keep the whole row but one accumulator per bin that OCCURS -- a bitmap of the
+// row's bins, its running popcount, and dense accumulators addressed through them -- and expands
+// to the full row (zeros elsewhere) when it writes it out.  Shared memory per row drops from
+// 4 * CIg bytes to CIg / 4 + 4 * sources, which keeps 24 warps per SM at CIg = 5120.
+template <bool COMPACT>
 __global__ void __launch_bounds__(256)
 inf_backward_weight_accum_kernel(const float* __restrict__ gout, const int* __restrict__ pos, Dims d,
                                  float* __restrict__ dst, int nbp, int vec_out) {
@@ -89,12 +95,23 @@ inf_backward_weight_accum_kernel(const float* __restrict__ gout, const int* __re
     const int rpc = blockDim.x >> 5;
     const int n_rows = d.CO, n_src = d.R, nb = d.CIg;
     const int row0 = blockIdx.x * rpc, row = row0 + warp;    // row = g * COg + o
-    float* acc = smem_f + (size_t)warp * nbp;
-    for (int i = lane * 4; i < nbp; i += 128) *reinterpret_cast<float4*>(acc + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+    // per-row area: the row itself, or (COMPACT) bitmap words | running popcounts | SB dense accumulators
+    const int nbw = (nb + 31) >> 5;
+    const int row_words = COMPACT ? 2 * ((nbw + 3) & ~3) + SB : nbp;
+    float* acc = smem_f + (size_t)warp * row_words;
+    unsigned* bits = reinterpret_cast<unsigned*>(acc);                 // COMPACT only
+    int* before = reinterpret_cast<int*>(acc) + ((nbw + 3) & ~3);      // COMPACT only
+    if (COMPACT) {
+        for (int i = lane; i < nbw; i += 32) bits[i] = 0u;
+        acc += 2 * ((nbw + 3) & ~3);
+        for (int i = lane; i < SB; i += 32) acc[i] = 0.f;
+    } else {
+        for (int i = lane * 4; i < nbp; i += 128) *reinterpret_cast<float4*>(acc + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     __syncwarp();
 
     // staging area behind the rows: [rpc][SB] pos words, [rpc][SB] signed values
-    int* spos = reinterpret_cast<int*>(smem_f + (size_t)rpc * nbp);
+    int* spos = reinterpret_cast<int*>(smem_f + (size_t)rpc * row_words);
     float* sval = reinterpret_cast<float*>(spos + (size_t)rpc * SB);
     for (int s0 = 0; s0 < n_src; s0 += SB) {
         const int cnt = min(SB, n_src - s0);
@@ -127,13 +144,39 @@ inf_backward_weight_accum_kernel(const float* __restrict__ gout, const int* __re
         if (row < n_rows) {
             const int* mp = spos + warp * SB;
             const float* mv = sval + warp * SB;
+            if (COMPACT) {
+                // which bins occur, and how many occurring bins lie before each 32-bin word
+                for (int e = lane; e < cnt; e += 32) {
+                    const int idx = mp[e] & 0x7fffffff;
+                    if (idx < nb) atomicOr(&bits[idx >> 5], 1u << (idx & 31));
+                }
+                __syncwarp();
+                int run = 0;
+                for (int w0 = 0; w0 < nbw; w0 += 32) {
+                    const int c = (w0 + lane < nbw) ? __popc(bits[w0 + lane]) : 0;
+                    int incl = c;
+#pragma unroll
+                    for (int sh = 1; sh < 32; sh <<= 1) {
+                        const int up = __shfl_up_sync(FULL, incl, sh);
+                        if (lane >= sh) incl += up;
+                    }
+                    if (w0 + lane < nbw) before[w0 + lane] = run + incl - c;
+                    run += __shfl_sync(FULL, incl, 31);
+                }
+                __syncwarp();
+            }
             // groups of 4 batches: the grouping of all four is issued before the first is added
             for (int b0 = 0; b0 * 32 < cnt; b0 += 4) {
                 Batch bt[4];
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     const int e = (b0 + u) * 32 + lane;
-                    bt[u] = classify(e < cnt ? (mp[e] & 0x7fffffff) : 0x7fffffff, e < cnt ? mv[e] : 0.f, nb, lane);
+                    int idx = e < cnt ? (mp[e] & 0x7fffffff) : 0x7fffffff;
+                    if (COMPACT) {
+                        // dense number of the bin among the occurring ones (equal bins, equal numbers)
+                        idx = idx < nb ? before[idx >> 5] + __popc(bits[idx >> 5] & ((1u << (idx & 31)) - 1u)) : 0x7fffffff;
+                    }
+                    bt[u] = classify(idx, e < cnt ? mv[e] : 0.f, COMPACT ? SB : nb, lane);
                 }
 #pragma unroll
                 for (int u = 0; u < 4; ++u)
@@ -144,6 +187,16 @@ inf_backward_weight_accum_kernel(const float* __restrict__ gout, const int* __re
     }
     if (row >= n_rows) return;
     float* out = dst + (size_t)row * nb;
+    if (COMPACT) {
+        __syncwarp();
+        for (int i0 = 0; i0 < nb; i0 += 32) {
+            const unsigned word = bits[i0 >> 5];
+            const int i = i0 + lane;
+            const float v = ((word >> lane) & 1u) ? acc[before[i0 >> 5] + __popc(word & ((1u << lane) - 1u))] : 0.f;
+            if (i < nb) out[i] = v;
+        }
+        return;
+    }
     if (vec_out) {
         for (int i = lane * 4; i < nb; i += 128)
             *reinterpret_cast<float4*>(out + i) = *reinterpret_cast<const float4*>(acc + i);
@@ -159,7 +212,12 @@ int inf_backward_weight_accum(const float* g, const int* pos, const Dims& d, flo
     if (d.HW != 1) return -1;
     const int nbp = (d.CIg + 3) & ~3;
     const size_t limit = 200 * 1024;
-    const size_t per_row = (size_t)nbp * 4 + (size_t)SB * 8;
+    // long rows with few sources, and enough rows for occupancy to matter: accumulators only for
+    // the bins that occur (measured at R = 512, CO = 5120: 61 us vs 76 us at CIg = 5120, but
+    // 59 us vs 50 us at CIg = 3072 and 23 us vs 16 us for the 10 rows of a classifier layer)
+    const bool compact = d.CIg >= 4096 && d.R <= SB && d.CO >= 1024;
+    const int nbw4 = (((d.CIg + 31) >> 5) + 3) & ~3;
+    const size_t per_row = (compact ? (size_t)(2 * nbw4 + SB) * 4 : (size_t)nbp * 4) + (size_t)SB * 8;
     if (per_row > limit) return -1;
     // Rows per CTA.  Neighbouring rows share the sectors of the strided sources: 8 rows use every
     // sector whole, but two CTAs per SM (one staging while the other adds) are worth more.
@@ -167,13 +225,13 @@ int inf_backward_weight_accum(const float* g, const int* pos, const Dims& d, flo
     while (rpc > 1 && (size_t)rpc * per_row > limit) rpc >>= 1;
     while (rpc > 2 && (size_t)rpc * per_row > 100 * 1024) rpc >>= 1;
     const size_t smem = (size_t)rpc * per_row;
+    auto kern = compact ? inf_backward_weight_accum_kernel<true> : inf_backward_weight_accum_kernel<false>;
     if (smem > 40 * 1024 &&
-        cudaFuncSetAttribute(inf_backward_weight_accum_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)limit) != cudaSuccess)
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)limit) != cudaSuccess)
         return LINF_ERR_LAUNCH;
     const int vec_out = ((d.CIg & 3) == 0 && (reinterpret_cast<uintptr_t>(gw) & 15u) == 0) ? 1 : 0;
     const int grid = (d.CO + rpc - 1) / rpc;
-    inf_backward_weight_accum_kernel<<<grid, 32 * rpc, smem, st>>>(g, pos, d, gw, nbp, vec_out);
+    kern<<<grid, 32 * rpc, smem, st>>>(g, pos, d, gw, nbp, vec_out);
     return launch_status();
 }
 

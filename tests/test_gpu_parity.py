@@ -466,7 +466,8 @@ def test_lp_shapes_that_leave_the_tiled_path(cuda, lib):
 
 
 @pytest.mark.parametrize("pattern", ["one_bin", "two_bins", "uniform", "out_of_range", "runs"])
-@pytest.mark.parametrize("shape", [(1100, 785, 96, 1), (40, 784, 1300, 1), (64, 60, 2048, 2), (513, 36, 520, 1)],
+@pytest.mark.parametrize("shape", [(1100, 785, 96, 1), (40, 784, 1300, 1), (64, 60, 2048, 2), (513, 36, 520, 1),
+                                   (300, 4100, 1024, 1), (64, 8192, 1030, 2)],
                          ids=lambda s: "B{}_CI{}_CO{}_G{}".format(*s))
 def test_inf_backward_synthetic_positions(cuda, lib, pattern, shape):
     """The ordered scatter on position patterns a forward pass rarely produces: every source of a
