@@ -2,7 +2,7 @@
 
 Run in a container that has the reference checkout (it is not needed to run the tests):
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py [--reference <checkout of zbh2047/L_inf-dist-net>]
 
 The script imports the reference's model/norm_dist.py (after registering an empty stand-in
 for its CUDA extension `norm_dist_cpp`, which that file imports unconditionally) and calls its
