@@ -73,6 +73,18 @@ def cpu_layer_rate(target_seconds=10.0):
     import oracle
     x, w, g = seeded_inputs(0)
     x, w, g = x.numpy(), w.numpy(), g.numpy()
+    # All host cores this process may use.  A launcher (torch.distributed.run) exports
+    # OMP_NUM_THREADS=1 to its workers and the OpenMP runtime has read that long before this point,
+    # so the thread count is set through the runtime's own call.
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = os.cpu_count() or 1
+    try:
+        import ctypes
+        ctypes.CDLL("libgomp.so.1").omp_set_num_threads(int(cores))
+    except OSError:
+        cores = int(os.environ.get("OMP_NUM_THREADS", cores))
 
     def run(nb):
         t0 = time.perf_counter()
@@ -87,7 +99,6 @@ def cpu_layer_rate(target_seconds=10.0):
     while dt < target_seconds and reps < 1000:        # repeat the slice until the time budget is used
         dt += run(nb)
         reps += 1
-    cores = int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
     return (reps * nb * DIN * DOUT / dt, cores,
             f"{reps} x forward+backward of {nb} of {B} batch rows, {dt:.2f} s in total")
 
