@@ -6,7 +6,7 @@ import subprocess
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "liblinfdist.so")
 CSRC = os.path.join(_HERE, "csrc")
-SOURCES = ["adamw.cu", "api.cu", "inf_forward.cu", "inf_bound.cu", "inf_backward.cu", "inf_backward_accum.cu", "lp.cu", "lp_tiled.cu", "no_alloc.cu", "peer_push.cu", "skinny.cu"]
+SOURCES = ["adamw.cu", "api.cu", "inf_forward.cu", "inf_bound.cu", "inf_backward.cu", "inf_backward_accum.cu", "inf_backward_direct.cu", "lp.cu", "lp_tiled.cu", "no_alloc.cu", "peer_push.cu", "skinny.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "--shared", "-Xcompiler", "-fPIC"]
 

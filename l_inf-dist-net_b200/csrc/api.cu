@@ -1,27 +1,88 @@
 // extern "C" surface of liblinfdist.so: argument validation, then the launchers.
 #include <math.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace linf {
 
+namespace {
+// per-device state of the library: read-only attributes and the helper stream
+struct DeviceSlot {
+    std::mutex lock;            // held by a SideLease for a whole fork ... join sequence
+    int sms = 0;
+    bool side_ready = false;
+    cudaStream_t side = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+};
+DeviceSlot g_slots[kMaxDevices];
+std::mutex g_attr_lock;
+
+int current_device() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return -1; }
+    return dev;
+}
+}  // namespace
+
 int sm_count() {
-    static int cached[16] = {};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return 148; }
-    if (dev < 0 || dev >= 16) dev = 0;
-    if (cached[dev] == 0) {
+    const int dev = current_device();
+    auto ask = [](int d) {
         int n = 0;
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+        if (d < 0 || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, d) != cudaSuccess || n <= 0) {
             cudaGetLastError();
             n = 148;
         }
-        cached[dev] = n;
+        return n;
+    };
+    if (dev < 0 || dev >= kMaxDevices) return ask(dev);
+    std::lock_guard<std::mutex> hold(g_attr_lock);
+    if (g_slots[dev].sms == 0) g_slots[dev].sms = ask(dev);
+    return g_slots[dev].sms;
+}
+
+SideLease::SideLease() : side_(nullptr) {
+    const int dev = current_device();
+    if (dev < 0 || dev >= kMaxDevices) return;
+    DeviceSlot* s = &g_slots[dev];
+    s->lock.lock();
+    if (!s->side_ready) {
+        if (cudaStreamCreateWithFlags(&s->side, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&s->fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&s->join, cudaEventDisableTiming) != cudaSuccess) {
+            cudaGetLastError();
+            s->lock.unlock();
+            return;
+        }
+        s->side_ready = true;
     }
-    return cached[dev];
+    side_ = s;
+}
+
+SideLease::~SideLease() {
+    if (side_ != nullptr) static_cast<DeviceSlot*>(side_)->lock.unlock();
+}
+
+cudaStream_t SideLease::stream() const { return static_cast<DeviceSlot*>(side_)->side; }
+
+int SideLease::fork(cudaStream_t from) {
+    DeviceSlot* s = static_cast<DeviceSlot*>(side_);
+    if (cudaEventRecord(s->fork, from) != cudaSuccess || cudaStreamWaitEvent(s->side, s->fork, 0) != cudaSuccess)
+        return LINF_ERR_LAUNCH;
+    return LINF_OK;
+}
+
+int SideLease::join(cudaStream_t into) {
+    DeviceSlot* s = static_cast<DeviceSlot*>(side_);
+    if (cudaEventRecord(s->join, s->side) != cudaSuccess || cudaStreamWaitEvent(into, s->join, 0) != cudaSuccess)
+        return LINF_ERR_LAUNCH;
+    return LINF_OK;
 }
 
 extern int inf_forward_variant;
+extern int inf_forward_tail;
+extern int inf_forward_split;
 int inf_forward_tma_gave_up();
 
 }  // namespace linf
@@ -56,6 +117,9 @@ const char* linf_error_string(int code) {
 // surface; not thread safe.
 int linf_tune_set(int key, int value) {
     if (key == 0 && value >= 0 && value < 16) { inf_forward_variant = value; return LINF_OK; }
+    if (key == 1 && (value == 0 || value == 1)) { inf_forward_tail = value; return LINF_OK; }
+    if (key == 3 && (value == 0 || value == 1)) { inf_backward_path = value; return LINF_OK; }
+    if (key == 4 && value >= 0 && value <= 2) { inf_forward_split = value; return LINF_OK; }
     if (key == 2) return inf_forward_tma_gave_up();   // 1 = a bounded wait of the TMA loader ran out since the library was loaded
     return LINF_ERR_DIMS;
 }

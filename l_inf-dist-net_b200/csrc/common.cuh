@@ -38,7 +38,30 @@ inline int launch_status() {
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Number of SMs of the current device (cached per device id; read-only after first use).
+// Device ids beyond the table (kMaxDevices) are asked from the runtime on every call.
+constexpr int kMaxDevices = 64;
 int sm_count();
+
+// The library owns one helper stream per device for work that runs beside the caller's stream
+// (the second kernel of the ordered backward).  A
+// SideLease holds the per-device lock from construction to destruction, so that the
+// record / wait pairs of one fork ... join sequence are never interleaved with those of another
+// host thread; kernels of several leases simply queue behind each other on the helper stream.
+class SideLease {
+public:
+    SideLease();
+    ~SideLease();
+    SideLease(const SideLease&) = delete;
+    SideLease& operator=(const SideLease&) = delete;
+    bool ok() const { return side_ != nullptr; }
+    cudaStream_t stream() const;
+    // helper stream waits for everything queued on `from` so far
+    int fork(cudaStream_t from);
+    // `into` waits for everything queued on the helper stream so far
+    int join(cudaStream_t into);
+private:
+    void* side_;
+};
 
 // ---- element addressing ------------------------------------------------------------
 // row r = b*HW + hw of group g, channel c of that group, in a [B, C, HW] tensor whose
@@ -86,6 +109,9 @@ int inf_backward_atomic(const float* g, const int* pos, const Dims& d, float* gx
                         cudaStream_t st);
 // sort-free ordered grad_weight for dense layers (inf_backward_accum.cu); -1 = shape not taken
 int inf_backward_weight_accum(const float* g, const int* pos, const Dims& d, float* gw, cudaStream_t st);
+// direct accumulation in shared memory for dense layers (inf_backward_direct.cu); -1 = shape not taken
+int inf_backward_input_direct(const float* g, const int* pos, const Dims& d, float* gx, cudaStream_t st);
+extern int inf_backward_path;
 int inf_backward_ordered_both(const float* g, const int* pos, const Dims& d, float* gx, float* gw,
                               cudaStream_t st);
 // few output channels per group (skinny.cu)

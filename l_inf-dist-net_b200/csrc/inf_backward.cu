@@ -23,11 +23,12 @@
 // for grad_weight a 32 x 32 tile is transposed through shared memory so that the lanes of a
 // warp run over the batch for one output channel, equal bins are combined inside the warp and
 // one atomic is issued per distinct bin.
-#include <mutex>
-
 #include "common.cuh"
 
 namespace linf {
+
+int inf_backward_path = 0;   // benchmarking knob: 1 = skip the direct-accumulation kernels
+
 namespace {
 
 constexpr unsigned FULL = 0xffffffffu;
@@ -528,8 +529,13 @@ int launch_ordered(const float* g, const int* pos, const Dims& d, float* dst, cu
     const int n_rows = (MODE == 0) ? d.R * d.G : d.CO;
     const int n_src = (MODE == 0) ? d.COg : d.R;
     const int nb = d.CIg;
+    if (MODE == 0 && inf_backward_path != 1) {
+        // dense layers with many bins per source: direct accumulation (inf_backward_direct.cu)
+        int rc = inf_backward_input_direct(g, pos, d, dst, st);
+        if (rc >= 0) return rc;
+    }
     if (MODE == 1) {
-        // dense layers: the sort-free kernel
+        // dense layers with longer rows: the warp-per-row kernel (inf_backward_accum.cu)
         int rc = inf_backward_weight_accum(g, pos, d, dst, st);
         if (rc >= 0) return rc;
     }
@@ -589,32 +595,20 @@ int inf_backward_weight(const float* g, const int* pos, const Dims& d, float* gw
 
 // Both ordered gradients.  The two kernels are independent and each of them is bound by the
 // latency of its sort phases rather than by throughput, so they are run side by side: grad_weight
-// on a helper stream that forks from, and joins back into, the caller's stream.  The helper stream
-// and its two events are created once per device and never destroyed.
+// on the library's helper stream, which forks from, and joins back into, the caller's stream.  The
+// lease keeps other host threads out of the helper stream's events until the join is queued.
 int inf_backward_ordered_both(const float* g, const int* pos, const Dims& d, float* gx, float* gw,
                               cudaStream_t st) {
-    struct Side { cudaStream_t stream; cudaEvent_t fork, join; bool ok; };
-    static Side sides[16] = {};
-    static std::mutex lock;
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return LINF_ERR_LAUNCH;
-    Side* s = &sides[dev];
-    {
-        std::lock_guard<std::mutex> hold(lock);
-        if (!s->ok) {
-            if (cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking) != cudaSuccess ||
-                cudaEventCreateWithFlags(&s->fork, cudaEventDisableTiming) != cudaSuccess ||
-                cudaEventCreateWithFlags(&s->join, cudaEventDisableTiming) != cudaSuccess)
-                return LINF_ERR_LAUNCH;
-            s->ok = true;
-        }
+    SideLease side;
+    if (!side.ok()) {            // no helper stream on this device: one after the other
+        const int rc = launch_ordered<1>(g, pos, d, gw, st);
+        const int rc2 = launch_ordered<0>(g, pos, d, gx, st);
+        return rc ? rc : rc2;
     }
-    if (cudaEventRecord(s->fork, st) != cudaSuccess || cudaStreamWaitEvent(s->stream, s->fork, 0) != cudaSuccess)
-        return LINF_ERR_LAUNCH;
-    int rc = launch_ordered<1>(g, pos, d, gw, s->stream);
+    if (side.fork(st) != LINF_OK) return LINF_ERR_LAUNCH;
+    const int rc = launch_ordered<1>(g, pos, d, gw, side.stream());
     const int rc2 = launch_ordered<0>(g, pos, d, gx, st);
-    if (cudaEventRecord(s->join, s->stream) != cudaSuccess || cudaStreamWaitEvent(st, s->join, 0) != cudaSuccess)
-        return LINF_ERR_LAUNCH;
+    if (side.join(st) != LINF_OK) return LINF_ERR_LAUNCH;
     return rc ? rc : rc2;
 }
 

@@ -24,6 +24,8 @@ namespace {
 
 constexpr unsigned FULL = 0xffffffffu;
 constexpr int SB = 512;          // sources per staged block
+constexpr int SBP = SB + 4;      // pitch of a row's staged block: neighbouring rows land 4 banks apart, so the
+                                 // staging stores of a warp (8 rows x 4 sources) touch 32 different banks
 
 // One batch of up to 32 sources, one per lane: bin `idx` (idx >= nb = no source / dropped) and
 // signed value `v`.
@@ -110,9 +112,9 @@ inf_backward_weight_accum_kernel(const float* __restrict__ gout, const int* __re
     }
     __syncwarp();
 
-    // staging area behind the rows: [rpc][SB] pos words, [rpc][SB] signed values
+    // staging area behind the rows: [rpc][SBP] pos words, [rpc][SBP] signed values
     int* spos = reinterpret_cast<int*>(smem_f + (size_t)rpc * row_words);
-    float* sval = reinterpret_cast<float*>(spos + (size_t)rpc * SB);
+    float* sval = reinterpret_cast<float*>(spos + (size_t)rpc * SBP);
     for (int s0 = 0; s0 < n_src; s0 += SB) {
         const int cnt = min(SB, n_src - s0);
         const int total = cnt * rpc;
@@ -135,15 +137,15 @@ inf_backward_weight_accum_kernel(const float* __restrict__ gout, const int* __re
                 const int q = q0 + u * blockDim.x;
                 if (q < total) {
                     const int j = q % rpc, e = q / rpc;
-                    spos[j * SB + e] = pp[u];
-                    sval[j * SB + e] = (pp[u] >= 0) ? -pg[u] : pg[u];     // grad_weight takes -s * g
+                    spos[j * SBP + e] = pp[u];
+                    sval[j * SBP + e] = (pp[u] >= 0) ? -pg[u] : pg[u];    // grad_weight takes -s * g
                 }
             }
         }
         __syncthreads();
         if (row < n_rows) {
-            const int* mp = spos + warp * SB;
-            const float* mv = sval + warp * SB;
+            const int* mp = spos + warp * SBP;
+            const float* mv = sval + warp * SBP;
             if (COMPACT) {
                 // which bins occur, and how many occurring bins lie before each 32-bin word
                 for (int e = lane; e < cnt; e += 32) {
@@ -217,7 +219,7 @@ int inf_backward_weight_accum(const float* g, const int* pos, const Dims& d, flo
     // 59 us vs 50 us at CIg = 3072 and 23 us vs 16 us for the 10 rows of a classifier layer)
     const bool compact = d.CIg >= 4096 && d.R <= SB && d.CO >= 1024;
     const int nbw4 = (((d.CIg + 31) >> 5) + 3) & ~3;
-    const size_t per_row = (compact ? (size_t)(2 * nbw4 + SB) * 4 : (size_t)nbp * 4) + (size_t)SB * 8;
+    const size_t per_row = (compact ? (size_t)(2 * nbw4 + SB) * 4 : (size_t)nbp * 4) + (size_t)SBP * 8;
     if (per_row > limit) return -1;
     // Rows per CTA.  Neighbouring rows share the sectors of the strided sources: 8 rows use every
     // sector whole, but two CTAs per SM (one staging while the other adds) are worth more.

@@ -265,15 +265,11 @@ int inf_bound(const float* xl, const float* xu, const float* w, const Dims& d,
     p.M = d.R; p.N = d.COg; p.K = d.CIg; p.G = d.G; p.lda = d.CI; p.ldo = d.CO;
     p.tiles_m = (d.R + BM - 1) / BM; p.tiles_n = (d.COg + BN - 1) / BN;
     p.KT = (d.CIg + BK - 1) / BK;
-    static bool configured[16] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 16 && !configured[dev]) {
-        if (cudaFuncSetAttribute(inf_bound_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 SMEM_BYTES) != cudaSuccess)
-            return LINF_ERR_LAUNCH;
-        configured[dev] = true;
-    }
+    // opting in to > 48 KB of dynamic shared memory is per function and per device; repeating it on
+    // every call is cheap and keeps the launcher free of per-device state
+    if (cudaFuncSetAttribute(inf_bound_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SMEM_BYTES) != cudaSuccess)
+        return LINF_ERR_LAUNCH;
     inf_bound_tiled_kernel<<<p.tiles_m * p.tiles_n * d.G, NT, SMEM_BYTES, st>>>(p);
     return launch_status();
 }

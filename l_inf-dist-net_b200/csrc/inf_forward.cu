@@ -10,13 +10,19 @@
 //     `max.f32` folds both |differences| into the running maximum.  Both are half-rate
 //     instructions, i.e. two issue cycles per pair of terms each -- the same two cycles per term
 //     as a scalar subtract plus a scalar max, but with half the instructions to fetch and decode.
-//     The arg-max is NOT tracked per term.  The loop only records, once per k-tile, which
-//     k-tile last raised the maximum; after the loop the winning k-tile alone is rescanned
-//     for the first index whose |difference| equals the maximum (strict ">" between tiles
-//     plus first-match inside a tile = lowest index among exact ties).
+//     The arg-max is NOT tracked per term.  The loop only records, once per tracking window (a
+//     k-tile or a fraction of one), which window last raised the maximum; after the loop the
+//     winning window alone is rescanned for the first index whose |difference| equals the
+//     maximum (strict ">" between windows plus first-match inside a window = lowest index among
+//     exact ties).
 //     With scratch memory the k-tiles of all output tiles are dealt out evenly to the CTAs that
 //     fit the GPU at once; an output tile cut by a CTA boundary is finished by whichever of its
 //     CTAs arrives last (ticket counter, nobody waits).
+//     Without k-splitting, a CTA is bound by latency, not by what its neighbours on the SM do
+//     (measured at B = 512, Din = 784, Dout = 5120: 444 tiles, three per SM, take 108 us; the 196
+//     tiles left over, one or two per SM, still take 87 us).  So when whole waves of tiles are
+//     followed by a partial one, the columns of the partial wave are cut into tiles of half the
+//     width and run as a second launch of twice as many CTAs, which fills the GPU again.
 //   * few outputs per group (skinny.cu): the reduction is spread over the threads of a CTA.
 //   * generic path (any G, HW, alignment): 32 x 32 tile, index tracked per term.
 #include <cuda.h>   // CUtensorMap and the enums of cuTensorMapEncodeTiled (types only: no libcuda link)
@@ -88,10 +94,11 @@ inf_forward_generic_kernel(const float* __restrict__ x, const float* __restrict_
 // =====================================================================================
 // Geometry of one kernel variant.  A thread owns 8 rows x TN columns; a warp (4 x 8 lanes)
 // owns 32 rows x 8*TN columns; a CTA has 2 warps along m and NT/64 along n.
-template <int NT_, int TN_, int BK_, int MINB_, int TRK_ = 1>
+template <int NT_, int TN_, int BK_, int MINB_, int TW_ = BK_>
 struct Geo {
     static constexpr int NT = NT_, TN = TN_, BK = BK_, MINB = MINB_;
-    static constexpr int TRK = TRK_;                    // k-tiles per arg-max tracking step
+    static constexpr int TW = TW_;                      // terms per arg-max tracking window
+    static constexpr int NSUB = BK / TW;                // tracking windows per k-tile (1, or even)
     static constexpr int BM = 64, BN = (NT / 64) * 8 * TN;
     static constexpr int NOUT = 8 * TN;                 // outputs per thread
     static constexpr int TILE_OUT = BM * BN;
@@ -99,6 +106,7 @@ struct Geo {
     static constexpr int STAGES = (BK <= 16) ? 4 : 3;
     static constexpr int STAGE_FLOATS = (BM + BN) * LD;
     static constexpr int SMEM_BYTES = STAGES * STAGE_FLOATS * 4;
+    static_assert(BK % TW == 0 && TW % 4 == 0 && (NSUB == 1 || NSUB % 2 == 0), "tracking window");
 };
 
 struct TiledParams {
@@ -110,6 +118,7 @@ struct TiledParams {
     int KT;                // k-tiles per output tile
     int n_cta;             // CTAs of the launch (units are dealt evenly to them)
     int slots_cta;         // CTAs the partial-result area was sized for
+    int tile0;             // whole mode: CTA b owns output tile tile0 + b
     int* tickets;          // one counter per output tile (split mode), else nullptr
     float* part_val;       // [slots_cta][2][TILE_OUT]
     int* part_cid;         // [slots_cta][2][TILE_OUT]
@@ -122,7 +131,7 @@ __device__ __forceinline__ long long unit_begin(const TiledParams& p, int c) {
 }
 
 // cp.async sources of one thread for the k-tiles of an output tile.  A thread always copies the
-// same 16-byte column `ch` of the same rows (32 rows apart) of x and of w; only k advances from
+// same 16-byte column `ch` of the same rows (RPP rows apart) of x and of w; only k advances from
 // tile to tile.  The row part of the address is worked out once per output tile and kept as a
 // 32-bit element offset (tensors of the tiled path have fewer than 2^31 elements), so that a
 // k-tile costs one add and one copy instruction per 16 bytes.
@@ -165,14 +174,14 @@ __device__ __forceinline__ void load_stage(float* stage, const TiledParams& p, c
     for (int u = 0; u < s.PB; ++u) cp_async16(Bs + u * s.RPP * GEO::LD, p.w + (size_t)(s.b[u] + kk), bytes);
 }
 
-// One k-tile of the (max, |a-b|) product for the 8 x TN sub-tile of this thread.
-// `in` holds the running maxima before the tile, `out` after it (they may alias).
-template <class GEO, int MODE>
+// Columns [4*K4B, 4*K4E) of one k-tile of the (max, |a-b|) product for the 8 x TN sub-tile of this
+// thread.  `in` holds the running maxima before, `out` after (they may alias).
+template <class GEO, int K4B, int K4E>
 __device__ __forceinline__ void tile_step(const float* __restrict__ As, const float* __restrict__ Bs,
                                           const float (&in)[GEO::NOUT], float (&out)[GEO::NOUT]) {
     constexpr int LD = GEO::LD, TN = GEO::TN;
 #pragma unroll
-    for (int k4 = 0; k4 < GEO::BK / 4; ++k4) {
+    for (int k4 = K4B; k4 < K4E; ++k4) {
         ulonglong2 bf[TN];
 #pragma unroll
         for (int j = 0; j < TN; ++j)
@@ -182,39 +191,47 @@ __device__ __forceinline__ void tile_step(const float* __restrict__ As, const fl
             const ulonglong2 af = *reinterpret_cast<const ulonglong2*>(As + (4 * i) * LD + k4 * 4);
 #pragma unroll
             for (int j = 0; j < TN; ++j) {
-                float a = (k4 == 0) ? in[i * TN + j] : out[i * TN + j];
+                float a = (k4 == K4B) ? in[i * TN + j] : out[i * TN + j];
                 float t0, t1, t2, t3;
-                if (MODE == 2) {
-                    unpack_f32x2(sub_f32x2(af.x, bf[j].x), t0, t1);
-                    unpack_f32x2(sub_f32x2(af.y, bf[j].y), t2, t3);
-                } else {
-                    float a0, a1, a2, a3, b0, b1, b2, b3;
-                    unpack_f32x2(af.x, a0, a1); unpack_f32x2(af.y, a2, a3);
-                    unpack_f32x2(bf[j].x, b0, b1); unpack_f32x2(bf[j].y, b2, b3);
-                    t0 = a0 - b0; t1 = a1 - b1; t2 = a2 - b2; t3 = a3 - b3;
-                }
-                if (MODE >= 1) {
-                    a = max3(a, fabsf(t0), fabsf(t1));
-                    a = max3(a, fabsf(t2), fabsf(t3));
-                } else {
-                    a = fmaxf(a, fabsf(t0)); a = fmaxf(a, fabsf(t1));
-                    a = fmaxf(a, fabsf(t2)); a = fmaxf(a, fabsf(t3));
-                }
+                unpack_f32x2(sub_f32x2(af.x, bf[j].x), t0, t1);
+                unpack_f32x2(sub_f32x2(af.y, bf[j].y), t2, t3);
+                a = max3(a, fabsf(t0), fabsf(t1));
+                a = max3(a, fabsf(t2), fabsf(t3));
                 out[i * TN + j] = a;
             }
         }
     }
 }
 
-// After a k-tile: every output whose maximum rose remembers the tile number.  Two 16-bit
-// tile numbers share a register; `ktdup` holds the tile number in both halves.
+// After a tracking window: every output whose maximum rose remembers the window number.  Two
+// 16-bit window numbers share a register; `dup` holds the number in both halves.
 template <int NOUT>
 __device__ __forceinline__ void note_raises(const float (&before)[NOUT], const float (&after)[NOUT],
-                                            unsigned (&cid)[NOUT / 2], unsigned ktdup) {
+                                            unsigned (&cid)[NOUT / 2], unsigned dup) {
 #pragma unroll
     for (int e = 0; e < NOUT; e += 2) {
-        if (after[e] > before[e]) cid[e >> 1] = __byte_perm(cid[e >> 1], ktdup, 0x3254);
-        if (after[e + 1] > before[e + 1]) cid[e >> 1] = __byte_perm(cid[e >> 1], ktdup, 0x7610);
+        if (after[e] > before[e]) cid[e >> 1] = __byte_perm(cid[e >> 1], dup, 0x3254);
+        if (after[e + 1] > before[e + 1]) cid[e >> 1] = __byte_perm(cid[e >> 1], dup, 0x7610);
+    }
+}
+
+// The NSUB tracking windows of one k-tile, ping-ponging between the two accumulator sets; NSUB is
+// even here, so the tile starts and ends in accA.
+template <class GEO, int S>
+__device__ __forceinline__ void tracked_windows(const float* __restrict__ As, const float* __restrict__ Bs,
+                                                float (&accA)[GEO::NOUT], float (&accB)[GEO::NOUT],
+                                                unsigned (&cid)[GEO::NOUT / 2], unsigned win0) {
+    if constexpr (S < GEO::NSUB) {
+        constexpr int K4B = S * GEO::TW / 4, K4E = (S + 1) * GEO::TW / 4;
+        const unsigned dup = (win0 + S) * 0x10001u;
+        if constexpr ((S & 1) == 0) {
+            tile_step<GEO, K4B, K4E>(As, Bs, accA, accB);
+            note_raises<GEO::NOUT>(accA, accB, cid, dup);
+        } else {
+            tile_step<GEO, K4B, K4E>(As, Bs, accB, accA);
+            note_raises<GEO::NOUT>(accB, accA, cid, dup);
+        }
+        tracked_windows<GEO, S + 1>(As, Bs, accA, accB, cid, win0);
     }
 }
 
@@ -229,17 +246,18 @@ __device__ __forceinline__ int cid_get(const unsigned (&cid)[H], int e) {
     return (e & 1) ? (int)(cid[e >> 1] >> 16) : (int)(cid[e >> 1] & 0xffffu);
 }
 
-// Finds the first index in the TRK k-tiles starting at tile `kt` whose |x - w| equals yv, and the
-// sign there.  (Scanning past the end of a split segment is harmless: a match inside comes first.)
-template <int BK, int TRK>
+// Finds the first index in tracking window `win` (TW terms) whose |x - w| equals yv, and the sign
+// there.  (A window that reaches past the end of a split segment is harmless: a match inside the
+// segment comes first.)
+template <int TW>
 __device__ __forceinline__ int resolve_pos(const float* __restrict__ xrow, const float* __restrict__ wrow,
-                                           int kt, int K, float yv) {
+                                           int win, int K, float yv) {
     if (!(yv > 0.f)) return 0;
-    const int kbase = kt * BK;
+    const int kbase = win * TW;
     int best = 0;
     float tb = 0.f;
 #pragma unroll
-    for (int q = BK * TRK / 4 - 1; q >= 0; --q) {
+    for (int q = TW / 4 - 1; q >= 0; --q) {
         if (kbase + 4 * q < K) {
             const float4 xv = __ldg(reinterpret_cast<const float4*>(xrow + kbase + 4 * q));
             const float4 wv = __ldg(reinterpret_cast<const float4*>(wrow + kbase + 4 * q));
@@ -256,7 +274,7 @@ __device__ __forceinline__ int resolve_pos(const float* __restrict__ xrow, const
 // ---- TMA loader (LOADER == 1) ---------------------------------------------------------------
 // One thread per CTA issues two tiled bulk copies per k-tile: (BK + 4) x BM floats of x and
 // (BK + 4) x BN floats of w.  The four extra columns are fetched only so that the rows land in
-// shared memory with the same 20-float pitch the cp.async loader produces (conflict-free 128-bit
+// shared memory with the same padded pitch the cp.async loader produces (conflict-free 128-bit
 // fragment loads without a swizzle); out-of-range rows and columns arrive as zeros.  Completion is
 // signalled on one mbarrier per stage; every wait is bounded: a thread that gives up sets
 // g_tma_gave_up, marks the CTA dead (later waits return at once) and the launch finishes with
@@ -300,12 +318,13 @@ __device__ __forceinline__ void tma_stage(float* stage, unsigned long long* bar,
     }
 }
 
-template <class GEO, int MODE, bool TRACK, int LOADER>
+template <class GEO, bool TRACK, int LOADER>
 __global__ void __launch_bounds__(GEO::NT, GEO::MINB)
 inf_forward_tiled_kernel(const __grid_constant__ TiledParams p) {
     constexpr int NT = GEO::NT, TN = GEO::TN, NOUT = GEO::NOUT, BK = GEO::BK, TILE_OUT = GEO::TILE_OUT;
     constexpr int BM = GEO::BM, BN = GEO::BN, STAGES = GEO::STAGES, STAGE_FLOATS = GEO::STAGE_FLOATS;
-    constexpr int NB = TRACK ? NOUT : 2;        // size of the second accumulator set / tile-number set
+    constexpr int NSUB = GEO::NSUB;
+    constexpr int NB = TRACK ? NOUT : 2;        // size of the second accumulator set / window-number set
     extern __shared__ __align__(16) float smem_raw[];
     __shared__ int s_last;
     __shared__ int s_dead;
@@ -331,15 +350,18 @@ inf_forward_tiled_kernel(const __grid_constant__ TiledParams p) {
 
     const int tiles_per_group = p.tiles_m * p.tiles_n;
     // Work of this CTA, in units of one k-tile of one output tile.  Split mode (tickets set): an
-    // even share of all units, whatever tiles it cuts through.  Whole mode: output tiles
-    // blockIdx.x, blockIdx.x + n_cta, ... (the launcher gives every tile a CTA of its own: starting
-    // the CTAs of an SM staggered so that their rescans do not coincide was measured and lost,
-    // 215 us against 207 us at B = 512, Din = 784, Dout = 5120).
+    // even share of all units, whatever tiles it cuts through.  Whole mode: output tile
+    // tile0 + blockIdx.x (the launcher gives every tile a CTA of its own: starting the CTAs of an SM
+    // staggered so that their rescans do not coincide was measured and lost, 215 us against 207 us
+    // at B = 512, Din = 784, Dout = 5120).
     const bool whole = p.tickets == nullptr;
-    long long u = whole ? (long long)blockIdx.x * p.KT : unit_begin(p, blockIdx.x);
-    const long long u_end = whole ? (long long)tiles_per_group * p.G * p.KT : unit_begin(p, blockIdx.x + 1);
+    long long u = whole ? (long long)(p.tile0 + (int)blockIdx.x) * p.KT : unit_begin(p, blockIdx.x);
+    const long long u_end = whole ? u + p.KT : unit_begin(p, blockIdx.x + 1);
     int seg = 0;
 
+    // (Doing a CTA's partial segments first and its whole tiles last, so that the merges of cut tiles
+    // happen early in the launch instead of behind every CTA's last k-tile, was measured and changed
+    // nothing: 195 us either way in split mode at B = 512, Din = 784, Dout = 5120.)
     while (u < u_end) {
         const int tile = (int)(u / p.KT);
         const int kt0 = (int)(u - (long long)tile * p.KT);
@@ -354,7 +376,7 @@ inf_forward_tiled_kernel(const __grid_constant__ TiledParams p) {
 #pragma unroll
         for (int e = 0; e < NOUT; ++e) accA[e] = 0.f;
 #pragma unroll
-        for (int e = 0; e < NB / 2; ++e) cid[e] = (unsigned)kt0 * 0x10001u;
+        for (int e = 0; e < NB / 2; ++e) cid[e] = (unsigned)(kt0 * NSUB) * 0x10001u;
 
         // ---- software pipeline over the k-tiles of this segment ----
         const StageSrc<GEO> src = stage_src<GEO>(p, g, m0, n0, tid);
@@ -374,58 +396,65 @@ inf_forward_tiled_kernel(const __grid_constant__ TiledParams p) {
                                                   &p.tm_x, &p.tm_w, g * p.K + (kt0 + s) * BK, m0, (kt0 + s) * BK, g * p.N + n0, tid);
             }
         }
-        constexpr int TRK = GEO::TRK;
-        for (int kt = kt0; kt < kt1; kt += 2 * TRK) {
+        // consume one k-tile: wait for its stage, refill the stage freed by the previous k-tile
+        auto next_stage = [&](int ktc) {
+            if constexpr (LOADER == 0) {
+                cp_async_wait<STAGES - 2>();
+            } else {
+                mbar_wait(&s_full[rd], (int)((filled / STAGES) & 1u), &s_dead);
+                ++filled;
+            }
+            __syncthreads();   // every thread is done with the stage about to be refilled
+            if constexpr (LOADER == 0) {
+                if (ktc + STAGES - 1 < kt1) load_stage<GEO>(smem + wr * STAGE_FLOATS, p, src, ktc + STAGES - 1);
+                cp_async_commit();
+            } else {
+                if (ktc + STAGES - 1 < kt1)
+                    tma_stage<GEO>(smem + wr * STAGE_FLOATS, &s_full[wr], &p.tm_x, &p.tm_w,
+                                   g * p.K + (ktc + STAGES - 1) * BK, m0, (ktc + STAGES - 1) * BK, g * p.N + n0, tid);
+            }
+        };
+        auto advance = [&]() {
+            rd = (rd + 1 == STAGES) ? 0 : rd + 1;
+            wr = (wr + 1 == STAGES) ? 0 : wr + 1;
+        };
+        if constexpr (TRACK && NSUB > 1) {
+            // several tracking windows per k-tile: every k-tile starts and ends in accA
+            for (int kt = kt0; kt < kt1; ++kt) {
+                next_stage(kt);
+                const float* As = smem + rd * STAGE_FLOATS + row_off * GEO::LD;
+                const float* Bs = smem + rd * STAGE_FLOATS + (BM + col_off) * GEO::LD;
+                tracked_windows<GEO, 0>(As, Bs, accA, accB, cid, (unsigned)(kt * NSUB));
+                advance();
+            }
+        } else {
+            // one tracking window per k-tile: two k-tiles per trip, accA -> accB -> accA
+            for (int kt = kt0; kt < kt1; kt += 2) {
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int kb = kt + h * TRK;             // first k-tile of this tracking step
-                if (kb < kt1) {
-#pragma unroll
-                    for (int s2 = 0; s2 < TRK; ++s2) {
-                        const int ktc = kb + s2;
-                        if (ktc < kt1) {
-                            if constexpr (LOADER == 0) {
-                                cp_async_wait<STAGES - 2>();
+                for (int h = 0; h < 2; ++h) {
+                    const int ktc = kt + h;
+                    if (ktc < kt1) {
+                        next_stage(ktc);
+                        const float* As = smem + rd * STAGE_FLOATS + row_off * GEO::LD;
+                        const float* Bs = smem + rd * STAGE_FLOATS + (BM + col_off) * GEO::LD;
+                        if constexpr (TRACK) {
+                            if (h == 0) {
+                                tile_step<GEO, 0, BK / 4>(As, Bs, accA, accB);
+                                note_raises<NOUT>(accA, accB, cid, (unsigned)ktc * 0x10001u);
                             } else {
-                                mbar_wait(&s_full[rd], (int)((filled / STAGES) & 1u), &s_dead);
-                                ++filled;
+                                tile_step<GEO, 0, BK / 4>(As, Bs, accB, accA);
+                                note_raises<NOUT>(accB, accA, cid, (unsigned)ktc * 0x10001u);
                             }
-                            __syncthreads();   // every thread is done with the stage about to be refilled
-                            if constexpr (LOADER == 0) {
-                                if (ktc + STAGES - 1 < kt1)
-                                    load_stage<GEO>(smem + wr * STAGE_FLOATS, p, src, ktc + STAGES - 1);
-                                cp_async_commit();
-                            } else {
-                                if (ktc + STAGES - 1 < kt1)
-                                    tma_stage<GEO>(smem + wr * STAGE_FLOATS, &s_full[wr], &p.tm_x, &p.tm_w,
-                                                   g * p.K + (ktc + STAGES - 1) * BK, m0, (ktc + STAGES - 1) * BK, g * p.N + n0, tid);
-                            }
-                            const float* As = smem + rd * STAGE_FLOATS + row_off * GEO::LD;
-                            const float* Bs = smem + rd * STAGE_FLOATS + (BM + col_off) * GEO::LD;
-                            if constexpr (TRACK) {
-                                if (h == 0) {
-                                    if (s2 == 0) tile_step<GEO, MODE>(As, Bs, accA, accB);
-                                    else tile_step<GEO, MODE>(As, Bs, accB, accB);
-                                } else {
-                                    if (s2 == 0) tile_step<GEO, MODE>(As, Bs, accB, accA);
-                                    else tile_step<GEO, MODE>(As, Bs, accA, accA);
-                                }
-                            } else {
-                                tile_step<GEO, MODE>(As, Bs, accA, accA);
-                            }
-                            rd = (rd + 1 == STAGES) ? 0 : rd + 1;
-                            wr = (wr + 1 == STAGES) ? 0 : wr + 1;
+                        } else {
+                            tile_step<GEO, 0, BK / 4>(As, Bs, accA, accA);
                         }
-                    }
-                    if constexpr (TRACK) {
-                        if (h == 0) note_raises<NOUT>(accA, accB, cid, (unsigned)kb * 0x10001u);
-                        else note_raises<NOUT>(accB, accA, cid, (unsigned)kb * 0x10001u);
-                    }
-                } else if (TRACK && h == 1) {
-                    // the last tracking step ended in the second set
-                    if constexpr (TRACK) {
+                        advance();
+                    } else if (TRACK && h == 1) {
+                        // the last k-tile ended in the second set
+                        if constexpr (TRACK) {
 #pragma unroll
-                        for (int e = 0; e < NOUT; ++e) accA[e] = accB[e];
+                            for (int e = 0; e < NOUT; ++e) accA[e] = accB[e];
+                        }
                     }
                 }
             }
@@ -503,14 +532,14 @@ inf_forward_tiled_kernel(const __grid_constant__ TiledParams p) {
                             p.y[o] = yv;
                             if constexpr (TRACK) {
                                 const float* wrow = p.w + ((size_t)g * p.N + n) * p.K;
-                                p.pos[o] = resolve_pos<BK, GEO::TRK>(xrow, wrow, cid_get(cid, i * TN + j), p.K, yv);
+                                p.pos[o] = resolve_pos<GEO::TW>(xrow, wrow, cid_get(cid, i * TN + j), p.K, yv);
                             }
                         }
                     }
                 }
             }
         }
-        u += whole ? (long long)p.n_cta * p.KT : (long long)(kt1 - kt0);
+        u += (long long)(kt1 - kt0);
         ++seg;   // only the first and the last segment of a CTA can be partial
     }
 }
@@ -518,27 +547,37 @@ inf_forward_tiled_kernel(const __grid_constant__ TiledParams p) {
 size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 // ---- variant table ------------------------------------------------------------------------
-struct Variant {
+struct Kernels {
     int bm, bn, bk, nt, min_blocks, smem;
+    void (*track)(const TiledParams);
+    void (*plain)(const TiledParams);
+};
+struct Variant {
+    Kernels main;      // 64 x 64 output tiles (8 x 4 outputs per thread), 3 CTAs per SM
+    Kernels tail;      // 64 x 32 output tiles (8 x 2 outputs per thread) for a partial last wave
     bool tma;
-    void (*kern_track)(const TiledParams);
-    void (*kern_plain)(const TiledParams);
 };
 
-template <class GEO, int MODE, int LOADER = 0>
-constexpr Variant make_variant() {
-    return Variant{GEO::BM, GEO::BN, GEO::BK, GEO::NT, GEO::MINB, GEO::SMEM_BYTES + (LOADER == 1 ? 128 : 0), LOADER == 1,
-                   inf_forward_tiled_kernel<GEO, MODE, true, LOADER>, inf_forward_tiled_kernel<GEO, MODE, false, LOADER>};
+template <class GEO, int LOADER = 0>
+constexpr Kernels make_kernels() {
+    return Kernels{GEO::BM, GEO::BN, GEO::BK, GEO::NT, GEO::MINB, GEO::SMEM_BYTES + (LOADER == 1 ? 128 : 0),
+                   inf_forward_tiled_kernel<GEO, true, LOADER>, inf_forward_tiled_kernel<GEO, false, LOADER>};
 }
 
+// All variants: CTAs of 128 threads.  Measured on B200, us per forward with arg-max at
+// B = 512, Dout = 5120 and Din = 784 / 1024 / 3072 / 5120 (whole tiles + tail launch below 1536, k-split above):
+//   0: 192 / 230 / 596 / 954      1: 190 / 237 / 620 / 997      2: 204 / 247 / 611 / 962
+// (the same kernels with the register budget of 4 CTAs per SM: 206-218 / 249-263 / 653-678 / 1022-1085).
 const Variant kVariants[] = {
-    make_variant<Geo<256, 4, 16, 2>, 2>(),   // 0: 8x4 per thread, 256 threads (64x128 tile), 2 CTAs/SM
-    make_variant<Geo<128, 8, 16, 2>, 2>(),   // 1: 8x8 per thread, 128 threads (64x128 tile), 2 CTAs/SM
-    make_variant<Geo<128, 4, 16, 3>, 2>(),   // 2: 8x4 per thread, 128 threads (64x64 tile), 3 CTAs/SM (default)
-    make_variant<Geo<128, 4, 16, 3>, 0>(),   // 3: as 2 with scalar subtract + 2-input max
-    make_variant<Geo<128, 4, 16, 3>, 1>(),   // 4: as 2 with scalar subtract + 3-input max
-    make_variant<Geo<128, 4, 16, 3>, 2, 1>(),// 5: as 2 with the TMA loader (measured 7-14 % slower than 2: the extra four
-                                             //    columns per row cost L2 traffic and one thread issues every copy)
+    // 0: 32-term k-tiles (3 stages), 8-term tracking windows (default)
+    {make_kernels<Geo<128, 4, 32, 3, 8>>(), make_kernels<Geo<128, 2, 32, 4, 8>>(), false},
+    // 1: 16-term k-tiles (4 stages), 8-term tracking windows
+    {make_kernels<Geo<128, 4, 16, 3, 8>>(), make_kernels<Geo<128, 2, 16, 4, 8>>(), false},
+    // 2: 16-term k-tiles, one tracking window per k-tile
+    {make_kernels<Geo<128, 4, 16, 3, 16>>(), make_kernels<Geo<128, 2, 16, 4, 16>>(), false},
+    // 3: as 2 with the TMA loader (measured 7-14 % slower than 2: the extra four columns per row cost
+    //    L2 traffic and one thread issues every copy)
+    {make_kernels<Geo<128, 4, 16, 3, 16>, 1>(), make_kernels<Geo<128, 2, 16, 4, 16>>(), true},
 };
 constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
 
@@ -552,12 +591,14 @@ int inf_forward_tma_gave_up() {
     return v;
 }
 
-int inf_forward_variant = 2;   // index into kVariants (benchmarking knob)
+int inf_forward_variant = 0;   // index into kVariants (benchmarking knob)
+int inf_forward_tail = 1;      // 1: a partial last wave runs as half-width tiles; 0: never
+int inf_forward_split = 0;     // 0: k-splitting by the rule of want_split; 1: whenever scratch is given; 2: never
 
-// Shapes the tiled path accepts.
+// Shapes the tiled path accepts (window numbers travel as 16 bits: at most 65535 windows per row).
 static bool tiled_ok(const float* x, const float* w, const Dims& d) {
     return d.HW == 1 && (d.CIg % 4) == 0 && aligned16(x) && aligned16(w) &&
-           d.COg >= 32 && (d.CIg + 15) / 16 < 65536 &&
+           d.COg >= 32 && (d.CIg + 7) / 8 < 65000 &&
            (size_t)d.R * d.CI < ((size_t)1 << 31) && (size_t)d.CO * d.CIg < ((size_t)1 << 31);
 }
 
@@ -567,7 +608,7 @@ static const Variant& cur_variant() {
 }
 
 static int tiled_tiles(const Dims& d, const Variant& v) {
-    return ((d.R + v.bm - 1) / v.bm) * ((d.COg + v.bn - 1) / v.bn) * d.G;
+    return ((d.R + v.main.bm - 1) / v.main.bm) * ((d.COg + v.main.bn - 1) / v.main.bn) * d.G;
 }
 
 // Splitting k-tiles across CTAs pays when whole tiles would leave a large part of the last
@@ -576,7 +617,9 @@ static int tiled_tiles(const Dims& d, const Variant& v) {
 // the k loop itself is short (measured: 217 us split vs 209 us unsplit at K = 784, 956 us vs
 // 1063 us at K = 5120).  With fewer tiles than CTA slots there is nothing to lose: split.
 static bool want_split(const Dims& d, const Variant& v) {
-    const int slots = v.min_blocks * sm_count();
+    if (inf_forward_split == 1) return true;
+    if (inf_forward_split == 2) return false;
+    const int slots = v.main.min_blocks * sm_count();
     const int tiles = tiled_tiles(d, v);
     const int waves = (tiles + slots - 1) / slots;
     if ((double)tiles / ((double)waves * slots) >= 0.9) return false;
@@ -587,9 +630,9 @@ size_t inf_forward_workspace(const Dims& d) {
     if (d.HW != 1 || (d.CIg % 4) != 0 || d.COg < 32) return 0;
     const Variant& v = cur_variant();
     if (!want_split(d, v)) return 0;
-    const size_t n_cta = (size_t)v.min_blocks * sm_count();
+    const size_t n_cta = (size_t)v.main.min_blocks * sm_count();
     return align256((size_t)tiled_tiles(d, v) * sizeof(int)) +
-           n_cta * 2 * v.bm * v.bn * (sizeof(float) + sizeof(int));
+           n_cta * 2 * v.main.bm * v.main.bn * (sizeof(float) + sizeof(int));
 }
 
 // ---- tensor maps for the TMA loader ----------------------------------------------------------
@@ -631,6 +674,16 @@ static bool tma_matrix(const float* base, size_t rows, size_t cols, size_t pitch
 // group are followed by the next group's columns, so a ragged last k-tile is only right for G = 1.
 static bool tma_shape_ok(const Dims& d) { return (d.G == 1 || d.CIg % 16 == 0) && d.CIg >= 32 && d.R >= 1; }
 
+static int launch_tiled(const Kernels& k, const TiledParams& p, bool track, cudaStream_t st) {
+    auto kern = track ? k.track : k.plain;
+    // opting in to > 48 KB of dynamic shared memory is per function and per device; it is cheap
+    // enough to repeat on every call and keeps the library free of mutable global state
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, k.smem) != cudaSuccess)
+        return LINF_ERR_LAUNCH;
+    kern<<<p.n_cta, k.nt, k.smem, st>>>(p);
+    return launch_status();
+}
+
 int inf_forward(const float* x, const float* w, const Dims& d, float* y, int* pos,
                 void* ws, size_t ws_bytes, cudaStream_t st) {
     if (!tiled_ok(x, w, d)) {
@@ -642,42 +695,62 @@ int inf_forward(const float* x, const float* w, const Dims& d, float* y, int* po
         return launch_status();
     }
     const Variant& v = cur_variant();
+    const Kernels* use = &v.main;
     TiledParams p;
     p.x = x; p.w = w; p.y = y; p.pos = pos;
     p.M = d.R; p.N = d.COg; p.K = d.CIg; p.G = d.G;
     p.lda = d.CI; p.ldo = d.CO;
-    p.tiles_m = (d.R + v.bm - 1) / v.bm; p.tiles_n = (d.COg + v.bn - 1) / v.bn;
-    p.KT = (d.CIg + v.bk - 1) / v.bk;
+    p.tiles_m = (d.R + use->bm - 1) / use->bm; p.tiles_n = (d.COg + use->bn - 1) / use->bn;
+    p.KT = (d.CIg + use->bk - 1) / use->bk;
     const int tiles = p.tiles_m * p.tiles_n * d.G;
     p.tickets = nullptr; p.part_val = nullptr; p.part_cid = nullptr;
     p.n_cta = tiles;       // whole mode: one CTA per output tile
     p.slots_cta = 0;
+    p.tile0 = 0;
+    const int slots = use->min_blocks * sm_count();
     const size_t need = inf_forward_workspace(d);
     if (ws != nullptr && need != 0) {
         if (ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 255u)) return LINF_ERR_WORKSPACE;
         const size_t tick_bytes = align256((size_t)tiles * sizeof(int));
         const long long total = (long long)tiles * p.KT;
-        p.slots_cta = v.min_blocks * sm_count();
+        p.slots_cta = slots;
         p.n_cta = (int)min((long long)p.slots_cta, total);
         p.tickets = reinterpret_cast<int*>(ws);
         p.part_val = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + tick_bytes);
-        p.part_cid = reinterpret_cast<int*>(p.part_val + (size_t)p.slots_cta * 2 * v.bm * v.bn);
+        p.part_cid = reinterpret_cast<int*>(p.part_val + (size_t)p.slots_cta * 2 * use->bm * use->bn);
         if (cudaMemsetAsync(p.tickets, 0, tick_bytes, st) != cudaSuccess) return LINF_ERR_LAUNCH;
     }
-    const Variant* use = &v;
     if (v.tma) {
         const bool ok = tma_shape_ok(d) &&
-                        tma_matrix(x, (size_t)d.R, (size_t)d.CI, (size_t)d.CI, v.bk + 4, v.bm, &p.tm_x) &&
-                        tma_matrix(w, (size_t)d.CO, (size_t)d.CIg, (size_t)d.CIg, v.bk + 4, v.bn, &p.tm_w);
-        if (!ok) use = &kVariants[2];           // same geometry with the cp.async loader
+                        tma_matrix(x, (size_t)d.R, (size_t)d.CI, (size_t)d.CI, use->bk + 4, use->bm, &p.tm_x) &&
+                        tma_matrix(w, (size_t)d.CO, (size_t)d.CIg, (size_t)d.CIg, use->bk + 4, use->bn, &p.tm_w);
+        if (!ok) use = &kVariants[2].main;      // same geometry with the cp.async loader
     }
-    auto kern = pos != nullptr ? use->kern_track : use->kern_plain;
-    // opting in to > 48 KB of dynamic shared memory is per function and per device; it is cheap
-    // enough to repeat on every call and keeps the library free of mutable global state
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, use->smem) != cudaSuccess)
-        return LINF_ERR_LAUNCH;
-    kern<<<p.n_cta, use->nt, use->smem, st>>>(p);
-    return launch_status();
+    // Whole tiles that end in a partial wave of CTAs (or never fill one): the columns of that
+    // partial wave are run as tiles of half the width by the tail kernels, twice as many CTAs.
+    // Only whole columns of tiles change hands, so the two launches cover disjoint column ranges.
+    if (p.tickets == nullptr && inf_forward_tail != 0 && d.G == 1 && v.tail.bk == use->bk) {
+        const int cols_main = ((tiles / slots) * slots) / p.tiles_m;     // tile columns of the whole waves
+        const int full = cols_main * p.tiles_m, rest = tiles - full;
+        const int tail_slots = v.tail.min_blocks * sm_count();
+        const int tail_tiles_n = (d.COg + v.tail.bn - 1) / v.tail.bn;
+        const int ratio = use->bn / v.tail.bn;
+        const int tail_ctas = (tail_tiles_n - ratio * cols_main) * p.tiles_m;
+        if (rest > 0 && rest * 10 <= slots * 8 && tail_ctas > 0 && tail_ctas <= tail_slots) {
+            int rc = LINF_OK;
+            if (full > 0) {
+                p.n_cta = full;
+                rc = launch_tiled(*use, p, pos != nullptr, st);
+                if (rc) return rc;
+            }
+            TiledParams q = p;
+            q.tiles_n = tail_tiles_n;
+            q.tile0 = ratio * cols_main * p.tiles_m;
+            q.n_cta = tail_ctas;
+            return launch_tiled(v.tail, q, pos != nullptr, st);
+        }
+    }
+    return launch_tiled(*use, p, pos != nullptr, st);
 }
 
 }  // namespace linf
