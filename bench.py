@@ -14,9 +14,16 @@ One JSON line is printed by rank 0.  `value` is measured with inputs resident in
 events around every step, an L2 flush between steps.  `e2e` repeats the measurement through the
 public Python API (norm_dist + autograd) with the step's inputs copied from pinned host memory
 and a scalar read back inside the timed region.  `roofline` relates the forward kernel to the
-FP32 non-FMA issue peak, `cpu_baseline` times the CPU checker (oracle/) on the host cores, and
-`train` / `train_tiny` report the CIFAR-shape and TinyImageNet-shape training steps (BASELINE
-configs[3] and [4]; data parallel over the same GPUs).
+FP32 non-FMA issue peak, `cpu_baseline` times the CPU checker (oracle/) on the host cores.
+Further objects of the same line (rank 0's GPU unless stated):
+  `lp`            BASELINE configs[1]: L_p layer 512 x 5120 x 5120, p in {8, 16, 64}, forward and both gradients
+  `bound`         BASELINE configs[2]: fused lower/upper bounds 512 x 3072 x 5120, groups 1 and 4
+  `gpu_baseline`  the reference's own CUDA kernels (compiled for sm_100a) on the headline workload
+  `certify`       the certification pass of the CIFAR-shape net (five layers, bounds only) and one PGD step
+  `train`, `train_p8`, `train_tiny`  CIFAR-shape (p = inf and p = 8) and TinyImageNet-shape training steps
+                  (BASELINE configs[3] and [4]; data parallel over all GPUs of the run, median step time)
+`--metric train` makes the CIFAR-shape training samples/s the top-level metric (the layer metric has no
+collective in it, so across GPUs it scales by construction; the training step is what exchanges gradients).
 
 `--impl reference` times the CPU restatement of the reference path on the host cores only.
 """
@@ -37,6 +44,8 @@ METRIC = "inf-dist layer distance-terms/s (fwd+bwd)"
 UNIT = "terms/s"
 B, DIN, DOUT = 512, 784, 5120
 WORKLOAD = "inf-dist layer fwd+bwd fp32 G=1: B=512/GPU, Din=784, Dout=5120 (BASELINE configs[0])"
+TRAIN_WORKLOAD = ("CIFAR-shape L_inf-dist net training step fp32: 3072-5120x4-10, MeanNorm, eps 8/255, batch 512/GPU, "
+                  "p = inf, data parallel (BASELINE configs[3])")
 SEED = 2020
 
 
@@ -50,7 +59,11 @@ def parse():
                     help="ordered = reproducible scatter (bit-exact to the checker); atomic = fused atomics")
     ap.add_argument("--no-train", action="store_true", help="skip the CIFAR-shape training-step measurement")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--train-steps", type=int, default=8)
+    ap.add_argument("--no-extra", action="store_true", help="skip the lp / bound / gpu_baseline / certify legs")
+    ap.add_argument("--train-steps", type=int, default=50)
+    ap.add_argument("--train-warmup", type=int, default=10)
+    ap.add_argument("--metric", default="layer", choices=["layer", "train"],
+                    help="layer: inf-dist layer terms/s is the top-level metric (default); train: CIFAR-shape train samples/s")
     return ap.parse_args()
 
 
@@ -101,6 +114,35 @@ def cpu_layer_rate(target_seconds=10.0):
         reps += 1
     return (reps * nb * DIN * DOUT / dt, cores,
             f"{reps} x forward+backward of {nb} of {B} batch rows, {dt:.2f} s in total")
+
+
+def cpu_torch_branch_rate(target_seconds=6.0):
+    """terms/s of the reference's pure-PyTorch distance branch, restated with the same torch ops
+    (model/norm_dist.py:52-57: broadcast difference [B, G, CO/G, CI/G, HW], inf-norm normaliser under
+    no_grad, norm of the normalised difference times the normaliser; backward through autograd), on a
+    batch chunk of 4 rows at a time so that the temporary stays below 100 MB."""
+    import torch
+    x, w, g = seeded_inputs(0)
+    torch.set_num_threads(max(1, len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)))
+    p = float("inf")
+
+    def run(rows):
+        t0 = time.perf_counter()
+        for r0 in range(0, rows, 4):
+            xi = x[r0:r0 + 4].clone().requires_grad_(True); wi = w.clone().requires_grad_(True)
+            y = xi.view(xi.size(0), 1, 1, -1, xi.size(2)) - wi.view(1, -1, wi.size(-1), 1)
+            with torch.no_grad():
+                normalize = torch.norm(y, dim=3, p=float("inf"), keepdim=True)
+            y = torch.norm(y / normalize, dim=3, p=p, keepdim=True) * normalize
+            y.view(y.size(0), -1, y.size(-1)).backward(g[r0:r0 + 4])
+        return time.perf_counter() - t0
+
+    run(4)
+    rows, dt = 0, 0.0
+    while dt < target_seconds and rows < B:
+        dt += run(8)
+        rows += 8
+    return rows * DIN * DOUT / dt, torch.get_num_threads(), f"forward+backward of {rows} of {B} batch rows in chunks of 4, {dt:.2f} s"
 
 
 def run_reference(args):
@@ -162,6 +204,122 @@ class ClockSampler:
         reasons = [n for k, n in enumerate(names) if any(len(r) >= 6 and r[2 + k] == "Active" for r in self.rows)]
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": reasons, "samples": len(sm)}
+
+
+def _timed_us(torch, fn, flush, n=10, warm=3):
+    """Median device time of fn() in microseconds (CUDA events on the current stream, L2 flushed between runs)."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(n):
+        flush.zero_()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record(); fn(); e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e3)
+    return statistics.median(ts)
+
+
+def extra_legs(torch, lib, dev, flush, lane_peak, hbm_peak):
+    """Configs 2 and 3, the reference's own kernels on config 1, the certification pass: rank 0's GPU only."""
+    import ctypes
+    from linfdist_b200 import _lib
+    stream = torch.cuda.current_stream().cuda_stream
+    gen = torch.Generator().manual_seed(SEED + 1)
+    out = {}
+
+    # ---- config 2: L_p layer, B = 512, Din = Dout = 5120, x, w, g ~ N(0,1) -------------------------
+    Bq, CI, CO = 512, 5120, 5120
+    x = torch.randn(Bq, CI, 1, generator=gen).to(dev); w = torch.randn(CO, CI, generator=gen).to(dev)
+    g = torch.randn(Bq, CO, 1, generator=gen).to(dev)
+    y = torch.empty(Bq, CO, 1, device=dev); gx = torch.empty_like(x); gw = torch.empty_like(w)
+    terms = Bq * CI * CO
+    lp = {"workload": "L_p layer fp32 G=1: B=512, Din=5120, Dout=5120 (BASELINE configs[1])", "unit": "terms/s",
+          "bound": "fp32-issue (integer p: the powers are multiplies on the FP32 pipe; no MUFU on this path)",
+          "ops_per_term": "forward: subtract, scale by 1/M, log2(p) squarings, add; each gradient: subtract, scale by 1/y, "
+                          "log2(p-2)+1 multiplies for s*|s|^(p-2), multiply by g, add"}
+    for p in (8.0, 16.0, 64.0):
+        a = (x.data_ptr(), w.data_ptr(), Bq, CO, CI, 1, 1)
+        t_f = _timed_us(torch, lambda: _lib.check(lib.linf_norm_dist_forward(*a, y.data_ptr(), p, stream), "lp forward"), flush, n=5, warm=2)
+        b = (g.data_ptr(), x.data_ptr(), w.data_ptr(), y.data_ptr(), Bq, CO, CI, 1, 1)
+        t_gx = _timed_us(torch, lambda: _lib.check(lib.linf_norm_dist_backward_input(*b, gx.data_ptr(), p, stream), "lp gx"), flush, n=5, warm=2)
+        t_gw = _timed_us(torch, lambda: _lib.check(lib.linf_norm_dist_backward_weight(*b, gw.data_ptr(), p, stream), "lp gw"), flush, n=5, warm=2)
+        import math
+        sq = int(math.log2(p))
+        ops_f, ops_b = 3 + sq, 4 + sq          # see ops_per_term; the forward also runs the max pass (2 ops per term)
+        lp[f"p{int(p)}"] = {
+            "us_forward": t_f, "us_grad_input": t_gx, "us_grad_weight": t_gw,
+            "fwd_terms_per_s": terms / (t_f * 1e-6), "fwd_bwd_terms_per_s": terms / ((t_f + t_gx + t_gw) * 1e-6),
+            "frac_fp32_issue_forward": (ops_f + 2) * terms / (t_f * 1e-6) / lane_peak,
+            "frac_fp32_issue_backward": 2 * ops_b * terms / ((t_gx + t_gw) * 1e-6) / lane_peak}
+    out["lp"] = lp
+    del x, w, g, y, gx, gw
+
+    # ---- config 3: interval bounds, B = 512, Din = 3072, Dout = 5120, groups 1 and 4 ----------------
+    Bq, CI, CO = 512, 3072, 5120
+    x = torch.rand(Bq, CI, 1, generator=gen)
+    lo = (x - 8 / 255).clamp(0, 1).to(dev); up = (x + 8 / 255).clamp(0, 1).to(dev)
+    bound = {"workload": "fused lower/upper bounds fp32: B=512, Din=3072, Dout=5120, eps 8/255 clamped to [0,1] (BASELINE configs[2])",
+             "unit": "terms/s", "bound": "fp32-issue",
+             "algorithmic": "6 fp32 non-FMA ops per term (2 subtracts, max(|tL|,|tU|), max into U, min(|tL|,|tU|), max into L)"}
+    for G in (1, 4):
+        w = torch.randn(CO, CI // G, generator=gen).to(dev)
+        yl = torch.empty(Bq, CO, 1, device=dev); yu = torch.empty_like(yl)
+        t = _timed_us(torch, lambda: _lib.check(lib.linf_inf_dist_bound_forward(
+            lo.data_ptr(), up.data_ptr(), w.data_ptr(), Bq, CO, CI, G, 1, yl.data_ptr(), yu.data_ptr(), stream), "bound"), flush)
+        tg = Bq * CO * (CI // G)
+        bound[f"G{G}"] = {"us": t, "terms_per_s": tg / (t * 1e-6), "frac_fp32_issue": 6.0 * tg / (t * 1e-6) / lane_peak}
+    out["bound"] = bound
+    del lo, up, w, yl, yu
+
+    # ---- the reference's own CUDA kernels on the headline workload ---------------------------------
+    ref_path = os.path.join(ROOT, "oracle", "_ref", "libref_norm_dist.so")
+    if os.path.exists(ref_path):
+        ref = ctypes.CDLL(ref_path)                      # test infrastructure, loaded for this leg only
+        x_h, w_h, g_h = seeded_inputs(0)
+        x, w, g = x_h.to(dev), w_h.to(dev), g_h.to(dev)
+        y = torch.empty(B, DOUT, 1, device=dev); pos = torch.empty(B, DOUT, 1, device=dev, dtype=torch.int32)
+        gx = torch.empty_like(x); gw = torch.empty_like(w)
+        P = lambda t: ctypes.c_void_p(t.data_ptr())
+        # the reference launches on the legacy default stream, which torch's current stream is here
+
+        def ref_fwd():
+            ref.ref_inf_dist_forward(P(x), P(w), B, DOUT, DIN, 1, 1, P(y), P(pos))
+
+        def ref_bwd():
+            gx.zero_(); gw.zero_()                       # model/norm_dist.py:34, 37: the caller zero-fills
+            ref.ref_inf_dist_backward_input(P(g), P(pos), B, DOUT, DIN, 1, 1, P(gx))
+            ref.ref_inf_dist_backward_weight(P(g), P(pos), B, DOUT, DIN, 1, 1, P(gw))
+
+        t_f = _timed_us(torch, ref_fwd, flush); t_b = _timed_us(torch, ref_bwd, flush)
+        out["gpu_baseline"] = {"what": "the reference's own kernels (model/inf_dist_cuda.cu) compiled for sm_100a, same inputs and timing",
+                               "workload": WORKLOAD, "us_forward": t_f, "us_backward": t_b,
+                               "value": B * DIN * DOUT / ((t_f + t_b) * 1e-6), "unit": UNIT}
+        del x, w, g, y, pos, gx, gw
+    else:
+        out["gpu_baseline"] = {"unavailable": "oracle/_ref/libref_norm_dist.so was not prebuilt"}
+
+    # ---- certification pass and one PGD step on the CIFAR-shape net ---------------------------------
+    import linfdist_b200 as L
+    from linfdist_b200.train_step import build_cifar_net
+    net = build_cifar_net(dev)
+    imgs = torch.rand(512, 3, 32, 32, generator=gen).to(dev); labels = torch.randint(0, 10, (512,), generator=gen).to(dev)
+    one, zero = torch.ones((), device=dev), torch.zeros((), device=dev)
+    t_c = _timed_us(torch, lambda: L.certify(net, imgs, labels, 8 / 255, one, zero), flush, n=5, warm=2)
+    terms_net = 512 * (3072 * 5120 + 3 * 5120 * 5120 + 5120 * 10)
+    atk = L.AttackPGD(net, 8 / 255, 2 / 255, 1, one, zero, random_start=False)
+    net.eval()
+    t_p = _timed_us(torch, lambda: atk.find(imgs, labels), flush, n=5, warm=2)
+    out["certify"] = {"workload": "CIFAR-shape net 3072-5120x4-10, B=512, eps 8/255: value + lower/upper through five layers "
+                                  "(main.py:166-194 semantics), then margins", "us": t_c, "samples_per_s": 512 / (t_c * 1e-6),
+                      "bound_terms_per_s": terms_net / (t_c * 1e-6),
+                      "note": "bound_terms_per_s counts the bound kernel's terms only; the pass also runs the value forward of every layer",
+                      "pgd_step_us": t_p, "pgd_note": "one step of AttackPGD: forward, cross entropy, backward to the input only"}
+    del net, imgs, labels
+    import gc
+    gc.collect(); torch.cuda.empty_cache()
+    return out
 
 
 def run_ours(args):
@@ -318,30 +476,39 @@ def run_ours(args):
     barrier()
     e2e_x_ms = max_over_ranks(b0.elapsed_time(b1) / e2e_steps)
 
-    # ---- training step (CIFAR-shape net, DDP) ----------------------------------------------
-    train = train_tiny = None
+    # ---- training steps (CIFAR-shape at p = inf and p = 8, TinyImageNet-shape; data parallel) -------
+    train = train_p8 = train_tiny = None
     if not args.no_train:
-        try:
-            from linfdist_b200.train_step import bench_train_step
-            train = bench_train_step(dev, world, rank, steps=args.train_steps, warmup=5)
-        except Exception as exc:                                           # never lose the layer line
-            train = {"error": repr(exc)}
-        try:
-            train_tiny = bench_train_step(dev, world, rank, steps=args.train_steps, warmup=5, config="tiny")
-        except Exception as exc:
-            train_tiny = {"error": repr(exc)}
+        from linfdist_b200.train_step import bench_train_step
 
-    clocks = sampler.stop() if sampler else None      # sampled across the layer, e2e and training legs
+        def leg(**kw):
+            try:
+                return bench_train_step(dev, world, rank, steps=args.train_steps, warmup=args.train_warmup, **kw)
+            except Exception as exc:                                       # never lose the layer line
+                return {"error": repr(exc)}
+
+        train = leg()
+        train_p8 = leg(p=8.0)
+        train_tiny = leg(config="tiny")
+
+    peaks = {}
+    pk_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(pk_path):
+        peaks = json.load(open(pk_path))
+    sm_max = float(peaks.get("sm_max_mhz", 1965.0))
+    props = torch.cuda.get_device_properties(dev)
+    lane_peak = props.multi_processor_count * 128 * sm_max * 1e6           # fp32 lane-ops per second
+    hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+    extra = {}
+    if rank == 0 and not args.no_extra:
+        try:
+            extra = extra_legs(torch, lib, dev, flush, lane_peak, hbm_peak)
+        except Exception as exc:                                           # never lose the layer line
+            extra = {"extra_error": repr(exc)}
+
+    clocks = sampler.stop() if sampler else None      # sampled across the layer, e2e, training and extra legs
     if rank == 0:
-        peaks = {}
-        pk_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-        if os.path.exists(pk_path):
-            peaks = json.load(open(pk_path))
-        sm_max = float(peaks.get("sm_max_mhz", 1965.0))
-        props = torch.cuda.get_device_properties(dev)
-        lane_peak = props.multi_processor_count * 128 * sm_max * 1e6       # fp32 lane-ops per second
         fwd_ops = 2.0 * terms / (t_fwd_max * 1e-3)                         # 1 subtract + 1 max per term
-        hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
         bwd_bytes = B * DOUT * 8 + (B * DIN + DOUT * DIN) * 4
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -371,11 +538,30 @@ def run_ours(args):
                                  "unit": "GB/s", "frac": bwd_bytes / (t_bwd * 1e-3) / 1e9 / hbm_peak},
             },
             "train": train,
+            "train_p8": train_p8,
             "train_tiny": train_tiny,
         }
+        line.update(extra)
+        if args.metric == "train" and train and "value" in train:
+            # the training step as the headline: its timed region copies every batch from pinned host
+            # memory and ends with the loss read back, so the end-to-end figure is the same measurement
+            line["layer"] = {"metric": METRIC, "value": value, "unit": UNIT, "ms_per_step": ms_step}
+            line.update({"metric": train["metric"], "value": train["value"], "unit": train["unit"],
+                         "ms_per_step": train["ms_per_step"], "steps": train["steps"], "warmup": args.train_warmup})
+            line["config"] = dict(line["config"], workload=TRAIN_WORKLOAD, exchange=train.get("exchange"))
+            line["e2e"] = {"value": train["value"], "unit": train["unit"], "h2d_bytes_per_step": 512 * 3 * 32 * 32 * 4 + 512 * 8,
+                           "d2h_bytes_per_step": 4, "ms_per_step": train["ms_per_step"]}
+            line["gpu_launches"] = train.get("launches_per_step", 0) * train["steps"]
         if not args.no_cpu:
             rate, cores, sample = cpu_layer_rate()
             line["cpu_baseline"] = {"value": rate, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+            try:
+                t_rate, t_threads, t_sample = cpu_torch_branch_rate()
+                line["cpu_baseline"]["torch_branch"] = {
+                    "value": t_rate, "unit": UNIT, "threads": t_threads, "sample": t_sample,
+                    "what": "the reference's pure-PyTorch distance branch (model/norm_dist.py:52-57) restated with the same torch ops"}
+            except Exception as exc:
+                line["cpu_baseline"]["torch_branch"] = {"error": repr(exc)}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

@@ -20,8 +20,11 @@
  *     are asynchronous with respect to the host;
  *   - the return value is 0 on success or one of the LINF_ERR_* codes; no entry point
  *     ever traps or asserts on the device;
- *   - the library keeps no mutable global state besides cached per-device attributes,
- *     so calls from several host threads are safe.
+ *   - besides cached per-device attributes the library keeps one helper stream per device
+ *     (linf_inf_dist_backward runs its second kernel there); its fork / join events are queued
+ *     under a per-device lock, so calls from several host threads are safe.  The tuning hook
+ *     linf_tune_set at the end of this header is the exception: it is process-wide and not
+ *     thread safe.
  */
 #ifndef LINFDIST_H_
 #define LINFDIST_H_
@@ -89,7 +92,9 @@ int linf_inf_dist_forward_ws(const float* input, const float* weight,
  *     holds (the need grows with the SM count of the GPU and, slowly, with the number of output
  *     tiles; on a 148-SM B200 every layer the library accepts fits).
  *   - The first call on each device looks up the device address of the array (with that device
- *     current); later calls on that device reuse it.
+ *     current); later calls on that device reuse it.  That first call may also be the moment the
+ *     CUDA runtime loads the library's device code onto that GPU, which is what makes the array
+ *     exist there; make it before any stream capture begins.
  *   - All calls on one GPU share the one array, and it keeps whatever the last call left there;
  *     the call clears the part that has to start at zero.  Two calls that overlap on the same
  *     GPU (different streams or threads) race on it: run them one after the other.
@@ -114,6 +119,44 @@ int linf_inf_dist_bound_forward(const float* input_lower, const float* input_upp
                                 const float* weight,
                                 int B, int CO, int CI, int G, int HW,
                                 float* output_lower, float* output_upper, void* stream);
+
+/*
+ * What follows an inf-dist layer at inference and certification time, folded into the kernel's store:
+ *     v' = (v - sub[c]) + add[c]      c = output channel; a NULL vector skips that step
+ *     v' = -v'                        if negate != 0
+ * sub is the running mean of the layer's mean-shift normalisation, add its bias (MeanNorm in eval mode
+ * and the bias add, model/norm_dist.py:95-97, :137-140, :150-155), negate the sign flip of the
+ * classifier layer (model/mlp.py:22).  The two operations are the fp32 subtraction and addition of
+ * the separate elementwise passes, in their order, so the result is theirs bit for bit.
+ *
+ * linf_inf_dist_forward_post: values only (no arg-max: the path that needs no gradient); workspace
+ * as for linf_inf_dist_forward_ws, or NULL / 0.
+ * linf_inf_dist_bound_forward_post: both bounds; with negate the outputs are also exchanged
+ * (output_lower receives the negated upper bound), as model/mlp.py:22 reorders them.
+ * No counterpart in the reference's binding, which runs these steps as torch operations.
+ */
+int linf_inf_dist_forward_post(const float* input, const float* weight,
+                               int B, int CO, int CI, int G, int HW,
+                               const float* sub, const float* add, int negate, float* output,
+                               void* workspace, size_t workspace_bytes, void* stream);
+int linf_inf_dist_bound_forward_post(const float* input_lower, const float* input_upper,
+                                     const float* weight,
+                                     int B, int CO, int CI, int G, int HW,
+                                     const float* sub, const float* add, int negate,
+                                     float* output_lower, float* output_upper, void* stream);
+
+/*
+ * Training-mode mean shift of a dense activation input[rows, cols] (rows = batch) in one launch:
+ *     mean[c] = (sum over rows, fixed order) / rows
+ *     running_mean[c] = running_mean[c] * (1 - momentum) + momentum * mean[c]     (skipped if NULL)
+ *     output[r, c] = input[r, c] - mean[c]                                       (output may be input)
+ * mean_out (cols floats) receives the means if not NULL.  Replaces the torch passes of MeanNorm.forward
+ * (model/norm_dist.py:85-97); with running_mean == NULL it is also that layer's backward
+ * (grad_in = grad_out - column mean of grad_out).  The mean agrees with another library's reduction to
+ * fp32 rounding (different summation order); subtraction and running-mean update are exact given it.
+ */
+int linf_mean_shift(const float* input, int rows, int cols, float* running_mean, float momentum,
+                    float* output, float* mean_out, void* stream);
 
 /*
  * grad_input[b, g*CI/G + idx, hw] = sum over o of (pos >= 0 ? +g : -g), g = grad_output[b,o,hw],
@@ -219,23 +262,21 @@ int linf_adamw_step(float* param, const float* grad, float* exp_avg, float* exp_
                     int rows, int cols, float p_norm, float lr, float beta1, float beta2,
                     float eps, float weight_decay, int step, void* stream);
 
+/* ---------------------------------------------------------------------------------
+ * tuning hook (benchmarks and tests only; no counterpart in the reference)
+ * --------------------------------------------------------------------------------- */
+
 /*
- * Host-side helpers of the copy-engine gradient exchange of the data-parallel training step
- * (ShardedCopyEngineStep in the Python package).  No counterpart in the reference, whose data
- * parallelism is torch's DistributedDataParallel over NCCL (main.py:195-199).
- *
- * linf_peer_push: queues n_copies asynchronous copies dst[i] <- src[i] of bytes[i] bytes on
- * `stream` (device memory of this GPU or memory of a peer mapped into this process; the copies run
- * on the copy engines, no kernel is launched), then n_flags writes of flag_value to the 32-bit words
- * flag_addr[i] (4-byte aligned, typically in the receivers' memory) as ONE batched stream memory
- * operation ordered behind the copies.  n_flags <= 64.
- * linf_flags_wait: makes `stream` wait, without a kernel, until every 32-bit word flag_addr[i] has
- * reached `value` (cyclic comparison (int)(*addr - value) >= 0).  The wait has no time limit: a
- * peer that never writes leaves the stream waiting, like a collective whose peer died.
+ * Process-wide switches between kernel variants that give identical results.  NOT thread safe, and
+ * key 0 changes what linf_inf_dist_forward_workspace_bytes answers: set it while no call is in flight.
+ *   key 0  tiled inf-dist forward variant (0 = default; the table is in csrc/inf_forward.cu)
+ *   key 1  1 = run a partial last wave of output tiles as half-width tiles (default), 0 = never
+ *   key 2  (value ignored) returns 1 if a bounded wait of the TMA-loader variant ever ran out, else 0
+ *   key 3  1 = skip the direct-accumulation grad_input kernel, 0 = use it where it applies (default)
+ *   key 4  k-splitting of the forward: 0 = by shape (default), 1 = whenever scratch is given, 2 = never
+ * Returns LINF_OK, the answer of key 2, or LINF_ERR_DIMS for an unknown key / value.
  */
-int linf_peer_push(int n_copies, void* const* dst, const void* const* src, const size_t* bytes,
-                   int n_flags, void* const* flag_addr, unsigned int flag_value, void* stream);
-int linf_flags_wait(int n_flags, void* const* flag_addr, unsigned int value, void* stream);
+int linf_tune_set(int key, int value);
 
 #ifdef __cplusplus
 }

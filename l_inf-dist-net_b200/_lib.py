@@ -6,7 +6,7 @@ import subprocess
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "liblinfdist.so")
 CSRC = os.path.join(_HERE, "csrc")
-SOURCES = ["adamw.cu", "api.cu", "inf_forward.cu", "inf_bound.cu", "inf_backward.cu", "inf_backward_accum.cu", "inf_backward_direct.cu", "lp.cu", "lp_tiled.cu", "no_alloc.cu", "peer_push.cu", "skinny.cu"]
+SOURCES = ["adamw.cu", "api.cu", "epilogue.cu", "inf_forward.cu", "inf_bound.cu", "inf_backward.cu", "inf_backward_accum.cu", "inf_backward_direct.cu", "lp.cu", "lp_tiled.cu", "no_alloc.cu", "skinny.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "--shared", "-Xcompiler", "-fPIC"]
 
@@ -23,14 +23,15 @@ _PROTOS = {
     "linf_inf_dist_forward_ws": [_F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F, _F, ctypes.c_size_t, _F],
     "linf_inf_dist_forward_noalloc": [_F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F, _F],
     "linf_inf_dist_bound_forward": [_F, _F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F, _F],
+    "linf_inf_dist_forward_post": [_F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F, _INT, _F, _F, ctypes.c_size_t, _F],
+    "linf_inf_dist_bound_forward_post": [_F, _F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F, _INT, _F, _F, _F],
+    "linf_mean_shift": [_F, _INT, _INT, _F, ctypes.c_float, _F, _F, _F],
     "linf_inf_dist_backward_input": [_F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F],
     "linf_inf_dist_backward_weight": [_F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F],
     "linf_inf_dist_backward": [_F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F, _F],
     "linf_inf_dist_backward_atomic": [_F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F, _F],
     "linf_adamw_step": [_F, _F, _F, _F, _INT, _INT, ctypes.c_float, ctypes.c_float, ctypes.c_float, ctypes.c_float,
                         ctypes.c_float, ctypes.c_float, _INT, _F],
-    "linf_peer_push": [_INT, _F, _F, _F, _INT, _F, ctypes.c_uint, _F],
-    "linf_flags_wait": [_INT, _F, ctypes.c_uint, _F],
     "linf_norm_dist_forward": [_F, _F, _INT, _INT, _INT, _INT, _INT, _F, ctypes.c_float, _F],
     "linf_norm_dist_backward_input": [_F, _F, _F, _F, _INT, _INT, _INT, _INT, _INT, _F, ctypes.c_float, _F],
     "linf_norm_dist_backward_weight": [_F, _F, _F, _F, _INT, _INT, _INT, _INT, _INT, _F, ctypes.c_float, _F],
@@ -39,8 +40,8 @@ _RESTYPE = {
     "linf_error_string": ctypes.c_char_p,
     "linf_inf_dist_forward_workspace_bytes": ctypes.c_size_t,
 }
-# the symbols include/linfdist.h declares (linf_tune_set is a benchmarking knob outside it)
-EXPORTED = [n for n in _PROTOS if n != "linf_tune_set"]
+# the symbols include/linfdist.h declares
+EXPORTED = list(_PROTOS)
 
 _lib = None
 

@@ -159,6 +159,36 @@ int linf_inf_dist_bound_forward(const float* input_lower, const float* input_upp
     return inf_bound(input_lower, input_upper, weight, d, output_lower, output_upper, as_stream(stream));
 }
 
+int linf_inf_dist_forward_post(const float* input, const float* weight, int B, int CO, int CI, int G, int HW,
+                               const float* sub, const float* add, int negate, float* output,
+                               void* workspace, size_t workspace_bytes, void* stream) {
+    if (!input || !weight || !output) return LINF_ERR_NULL;
+    Dims d;
+    int rc = make_dims(B, CO, CI, G, HW, &d);
+    if (rc) return rc;
+    const Post post{sub, add, negate ? 1 : 0};
+    return inf_forward(input, weight, d, output, nullptr, workspace, workspace_bytes, as_stream(stream), post);
+}
+
+int linf_inf_dist_bound_forward_post(const float* input_lower, const float* input_upper, const float* weight,
+                                     int B, int CO, int CI, int G, int HW,
+                                     const float* sub, const float* add, int negate,
+                                     float* output_lower, float* output_upper, void* stream) {
+    if (!input_lower || !input_upper || !weight || !output_lower || !output_upper) return LINF_ERR_NULL;
+    Dims d;
+    int rc = make_dims(B, CO, CI, G, HW, &d);
+    if (rc) return rc;
+    const Post post{sub, add, negate ? 1 : 0};
+    return inf_bound(input_lower, input_upper, weight, d, output_lower, output_upper, as_stream(stream), post);
+}
+
+int linf_mean_shift(const float* input, int rows, int cols, float* running_mean, float momentum,
+                    float* output, float* mean_out, void* stream) {
+    if (!input || !output) return LINF_ERR_NULL;
+    if (rows <= 0 || cols <= 0 || (long long)rows * cols > 0x7fffffffLL) return LINF_ERR_DIMS;
+    return mean_shift(input, rows, cols, running_mean, momentum, output, mean_out, as_stream(stream));
+}
+
 int linf_inf_dist_backward_input(const float* grad_output, const int* pos, int B, int CO, int CI, int G, int HW,
                                  float* grad_input, void* stream) {
     if (!grad_output || !pos || !grad_input) return LINF_ERR_NULL;

@@ -97,12 +97,31 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
 
+// ---- optional per-output-channel epilogue of the forward and bound kernels -------------------
+//   v' = (v - sub[c]) + add[c]      either vector may be null: that step is skipped
+//   v' = -v'                        if negate; the bound kernels then also exchange lower and upper
+// c is the output channel (0 .. CO-1).  This is what follows an inf-dist layer in eval mode -- the
+// mean shift by the running mean, the bias, the sign flip of the classifier layer -- applied in the
+// same two fp32 operations and the same order as the separate elementwise passes it replaces.
+struct Post {
+    const float* sub; const float* add; int negate;
+};
+__device__ __forceinline__ float post_apply(const Post& q, float v, int c) {
+    if (q.sub != nullptr) v = v - __ldg(q.sub + c);
+    if (q.add != nullptr) v = v + __ldg(q.add + c);
+    return q.negate ? -v : v;
+}
+inline Post no_post() { return Post{nullptr, nullptr, 0}; }
+
 // ---- launchers implemented in the .cu files -----------------------------------------
 int inf_forward(const float* x, const float* w, const Dims& d, float* y, int* pos,
-                void* ws, size_t ws_bytes, cudaStream_t st);
+                void* ws, size_t ws_bytes, cudaStream_t st, const Post& post = Post{nullptr, nullptr, 0});
 size_t inf_forward_workspace(const Dims& d);
 int inf_bound(const float* xl, const float* xu, const float* w, const Dims& d,
-              float* yl, float* yu, cudaStream_t st);
+              float* yl, float* yu, cudaStream_t st, const Post& post = Post{nullptr, nullptr, 0});
+// batch-mean shift of a [rows, cols] activation (epilogue.cu)
+int mean_shift(const float* in, int rows, int cols, float* running_mean, float momentum, float* out,
+               float* mean_out, cudaStream_t st);
 int inf_backward_input(const float* g, const int* pos, const Dims& d, float* gx, cudaStream_t st);
 int inf_backward_weight(const float* g, const int* pos, const Dims& d, float* gw, cudaStream_t st);
 int inf_backward_atomic(const float* g, const int* pos, const Dims& d, float* gx, float* gw,
@@ -116,9 +135,10 @@ int inf_backward_ordered_both(const float* g, const int* pos, const Dims& d, flo
                               cudaStream_t st);
 // few output channels per group (skinny.cu)
 bool skinny_ok(const Dims& d, const void* a, const void* b, const void* c);
-int inf_forward_skinny(const float* x, const float* w, const Dims& d, float* y, int* pos, cudaStream_t st);
+int inf_forward_skinny(const float* x, const float* w, const Dims& d, float* y, int* pos, cudaStream_t st,
+                       const Post& post);
 int inf_bound_skinny(const float* xl, const float* xu, const float* w, const Dims& d, float* yl, float* yu,
-                     cudaStream_t st);
+                     cudaStream_t st, const Post& post);
 // register-tiled finite-p kernels for dense, aligned layers (lp_tiled.cu)
 bool lp_tiled_ok(const Dims& d, const void* a, const void* b, const void* c, const void* e, const void* f);
 int lp_forward_tiled(const float* x, const float* w, const Dims& d, float* y, float p, cudaStream_t st);

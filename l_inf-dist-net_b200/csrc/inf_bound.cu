@@ -40,7 +40,7 @@ template <bool ROW_FAST>
 __global__ void __launch_bounds__(256)
 inf_bound_generic_kernel(const float* __restrict__ xl, const float* __restrict__ xu,
                          const float* __restrict__ w, Dims d,
-                         float* __restrict__ yl, float* __restrict__ yu) {
+                         float* __restrict__ yl, float* __restrict__ yu, Post post) {
     __shared__ float ls[GT][GT + 1], us[GT][GT + 1], ws[GT][GT + 1];
     const int tid = threadIdx.x, tx = tid & 31, ty = tid >> 5;
     const int g = blockIdx.z, r0 = blockIdx.x * GT, c0 = blockIdx.y * GT;
@@ -74,8 +74,9 @@ inf_bound_generic_kernel(const float* __restrict__ xl, const float* __restrict__
             int r = r0 + ty + 8 * j;
             if (r < d.R) {
                 size_t o = act_index(r, g, c, d.COg, d.G, d.HW);
-                yl[o] = L[j];
-                yu[o] = U[j];
+                const float lo = post_apply(post, L[j], g * d.COg + c), up = post_apply(post, U[j], g * d.COg + c);
+                yl[o] = post.negate ? up : lo;
+                yu[o] = post.negate ? lo : up;
             }
         }
     }
@@ -92,6 +93,7 @@ constexpr int SMEM_BYTES = STAGES * STAGE_FLOATS * 4;
 struct BoundParams {
     const float* xl; const float* xu; const float* w; float* yl; float* yu;
     int M, N, K, G, lda, ldo, tiles_m, tiles_n, KT;
+    Post post;             // per-channel epilogue of the stored bounds (all null: none)
 };
 
 __device__ __forceinline__ void load_stage(float* stage, const BoundParams& p, int g, int m0, int n0,
@@ -238,8 +240,10 @@ inf_bound_tiled_kernel(const BoundParams p) {
                 const int n = n0 + col_off + 8 * j;
                 if (n < p.N) {
                     const size_t o = (size_t)m * p.ldo + (size_t)g * p.N + n;
-                    p.yl[o] = accL[i * TN + j];
-                    p.yu[o] = accU[i * TN + j];
+                    const float lo = post_apply(p.post, accL[i * TN + j], g * p.N + n);
+                    const float up = post_apply(p.post, accU[i * TN + j], g * p.N + n);
+                    p.yl[o] = p.post.negate ? up : lo;       // a negated upper bound is the new lower bound
+                    p.yu[o] = p.post.negate ? lo : up;
                 }
             }
         }
@@ -249,20 +253,21 @@ inf_bound_tiled_kernel(const BoundParams p) {
 }  // namespace
 
 int inf_bound(const float* xl, const float* xu, const float* w, const Dims& d,
-              float* yl, float* yu, cudaStream_t st) {
+              float* yl, float* yu, cudaStream_t st, const Post& post) {
     const bool tiled = d.HW == 1 && (d.CIg % 4) == 0 && aligned16(xl) && aligned16(xu) && aligned16(w) &&
                        d.COg >= 32;
     if (!tiled) {
-        if (skinny_ok(d, xl, xu, w)) return inf_bound_skinny(xl, xu, w, d, yl, yu, st);
+        if (skinny_ok(d, xl, xu, w)) return inf_bound_skinny(xl, xu, w, d, yl, yu, st, post);
         dim3 grid((d.R + GT - 1) / GT, (d.COg + GT - 1) / GT, d.G);
         if (grid.y > 65535u || grid.z > 65535u) return LINF_ERR_DIMS;
-        if (d.HW > 1) inf_bound_generic_kernel<true><<<grid, 256, 0, st>>>(xl, xu, w, d, yl, yu);
-        else inf_bound_generic_kernel<false><<<grid, 256, 0, st>>>(xl, xu, w, d, yl, yu);
+        if (d.HW > 1) inf_bound_generic_kernel<true><<<grid, 256, 0, st>>>(xl, xu, w, d, yl, yu, post);
+        else inf_bound_generic_kernel<false><<<grid, 256, 0, st>>>(xl, xu, w, d, yl, yu, post);
         return launch_status();
     }
     BoundParams p;
     p.xl = xl; p.xu = xu; p.w = w; p.yl = yl; p.yu = yu;
     p.M = d.R; p.N = d.COg; p.K = d.CIg; p.G = d.G; p.lda = d.CI; p.ldo = d.CO;
+    p.post = post;
     p.tiles_m = (d.R + BM - 1) / BM; p.tiles_n = (d.COg + BN - 1) / BN;
     p.KT = (d.CIg + BK - 1) / BK;
     // opting in to > 48 KB of dynamic shared memory is per function and per device; repeating it on

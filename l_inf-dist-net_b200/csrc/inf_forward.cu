@@ -41,7 +41,7 @@ constexpr int GT = 32;  // generic tile edge
 template <bool ROW_FAST>
 __global__ void __launch_bounds__(256)
 inf_forward_generic_kernel(const float* __restrict__ x, const float* __restrict__ w, Dims d,
-                           float* __restrict__ y, int* __restrict__ pos) {
+                           float* __restrict__ y, int* __restrict__ pos, Post post) {
     __shared__ float xs[GT][GT + 1];  // [k][row]
     __shared__ float ws[GT][GT + 1];  // [k][col]
     const int tid = threadIdx.x, tx = tid & 31, ty = tid >> 5;
@@ -82,7 +82,7 @@ inf_forward_generic_kernel(const float* __restrict__ x, const float* __restrict_
             int r = r0 + ty + 8 * j;
             if (r < d.R) {
                 size_t o = act_index(r, g, c, d.COg, d.G, d.HW);
-                y[o] = best[j];
+                y[o] = post_apply(post, best[j], g * d.COg + c);
                 if (pos) pos[o] = arg[j];
             }
         }
@@ -119,6 +119,7 @@ struct TiledParams {
     int n_cta;             // CTAs of the launch (units are dealt evenly to them)
     int slots_cta;         // CTAs the partial-result area was sized for
     int tile0;             // whole mode: CTA b owns output tile tile0 + b
+    Post post;             // per-channel epilogue of the stored values (all null: none)
     int* tickets;          // one counter per output tile (split mode), else nullptr
     float* part_val;       // [slots_cta][2][TILE_OUT]
     int* part_cid;         // [slots_cta][2][TILE_OUT]
@@ -529,7 +530,7 @@ inf_forward_tiled_kernel(const __grid_constant__ TiledParams p) {
                         if (n < p.N) {
                             const float yv = accA[i * TN + j];
                             const size_t o = (size_t)m * p.ldo + (size_t)g * p.N + n;
-                            p.y[o] = yv;
+                            p.y[o] = post_apply(p.post, yv, g * p.N + n);
                             if constexpr (TRACK) {
                                 const float* wrow = p.w + ((size_t)g * p.N + n) * p.K;
                                 p.pos[o] = resolve_pos<GEO::TW>(xrow, wrow, cid_get(cid, i * TN + j), p.K, yv);
@@ -685,13 +686,13 @@ static int launch_tiled(const Kernels& k, const TiledParams& p, bool track, cuda
 }
 
 int inf_forward(const float* x, const float* w, const Dims& d, float* y, int* pos,
-                void* ws, size_t ws_bytes, cudaStream_t st) {
+                void* ws, size_t ws_bytes, cudaStream_t st, const Post& post) {
     if (!tiled_ok(x, w, d)) {
-        if (skinny_ok(d, x, w, nullptr)) return inf_forward_skinny(x, w, d, y, pos, st);
+        if (skinny_ok(d, x, w, nullptr)) return inf_forward_skinny(x, w, d, y, pos, st, post);
         dim3 grid((d.R + GT - 1) / GT, (d.COg + GT - 1) / GT, d.G);
         if (grid.y > 65535u || grid.z > 65535u) return LINF_ERR_DIMS;
-        if (d.HW > 1) inf_forward_generic_kernel<true><<<grid, 256, 0, st>>>(x, w, d, y, pos);
-        else inf_forward_generic_kernel<false><<<grid, 256, 0, st>>>(x, w, d, y, pos);
+        if (d.HW > 1) inf_forward_generic_kernel<true><<<grid, 256, 0, st>>>(x, w, d, y, pos, post);
+        else inf_forward_generic_kernel<false><<<grid, 256, 0, st>>>(x, w, d, y, pos, post);
         return launch_status();
     }
     const Variant& v = cur_variant();
@@ -707,6 +708,7 @@ int inf_forward(const float* x, const float* w, const Dims& d, float* y, int* po
     p.n_cta = tiles;       // whole mode: one CTA per output tile
     p.slots_cta = 0;
     p.tile0 = 0;
+    p.post = post;
     const int slots = use->min_blocks * sm_count();
     const size_t need = inf_forward_workspace(d);
     if (ws != nullptr && need != 0) {

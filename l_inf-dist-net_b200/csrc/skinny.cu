@@ -17,7 +17,7 @@ constexpr unsigned FULL = 0xffffffffu;
 template <int NMAX, int R>
 __global__ void __launch_bounds__(256)
 inf_forward_skinny_kernel(const float* __restrict__ x, const float* __restrict__ w, Dims d,
-                          float* __restrict__ y, int* __restrict__ pos) {
+                          float* __restrict__ y, int* __restrict__ pos, Post post) {
     __shared__ float s_t[8][R][NMAX];
     __shared__ int s_i[8][R][NMAX];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -88,7 +88,7 @@ inf_forward_skinny_kernel(const float* __restrict__ x, const float* __restrict__
             }
             const size_t o = (size_t)(r0 + r) * d.CO + (size_t)g * N + n;
             const float yv = fabsf(t);
-            y[o] = yv;
+            y[o] = post_apply(post, yv, g * N + n);
             if (pos) pos[o] = (yv > 0.f) ? (i | (t < 0.f ? (int)0x80000000 : 0)) : 0;
         }
     }
@@ -98,7 +98,7 @@ inf_forward_skinny_kernel(const float* __restrict__ x, const float* __restrict__
 template <int NMAX, int R>
 __global__ void __launch_bounds__(256)
 inf_bound_skinny_kernel(const float* __restrict__ xl, const float* __restrict__ xu,
-                        const float* __restrict__ w, Dims d, float* __restrict__ yl, float* __restrict__ yu) {
+                        const float* __restrict__ w, Dims d, float* __restrict__ yl, float* __restrict__ yu, Post post) {
     __shared__ float s_l[8][R][NMAX], s_u[8][R][NMAX];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int wpc = blockDim.x >> 5;
@@ -165,26 +165,27 @@ inf_bound_skinny_kernel(const float* __restrict__ xl, const float* __restrict__ 
             float l = s_l[0][r][n], u = s_u[0][r][n];
             for (int wv = 1; wv < wpc; ++wv) { l = fmaxf(l, s_l[wv][r][n]); u = fmaxf(u, s_u[wv][r][n]); }
             const size_t o = (size_t)(r0 + r) * d.CO + (size_t)g * N + n;
-            yl[o] = l; yu[o] = u;
+            l = post_apply(post, l, g * N + n); u = post_apply(post, u, g * N + n);
+            yl[o] = post.negate ? u : l; yu[o] = post.negate ? l : u;
         }
     }
 }
 
 template <int NMAX, int R>
-int launch_fwd(const float* x, const float* w, const Dims& d, float* y, int* pos, cudaStream_t st) {
+int launch_fwd(const float* x, const float* w, const Dims& d, float* y, int* pos, cudaStream_t st, const Post& post) {
     const int items = ((d.R + R - 1) / R) * d.G;
     // warps that share a row block: as many as there are 128-float chunks to hand out, up to 8
     int wpc = min(8, max(1, d.CIg / 512));
-    inf_forward_skinny_kernel<NMAX, R><<<items, 32 * wpc, 0, st>>>(x, w, d, y, pos);
+    inf_forward_skinny_kernel<NMAX, R><<<items, 32 * wpc, 0, st>>>(x, w, d, y, pos, post);
     return launch_status();
 }
 
 template <int NMAX, int R>
 int launch_bound(const float* xl, const float* xu, const float* w, const Dims& d, float* yl, float* yu,
-                 cudaStream_t st) {
+                 cudaStream_t st, const Post& post) {
     const int items = ((d.R + R - 1) / R) * d.G;
     int wpc = min(8, max(1, d.CIg / 512));
-    inf_bound_skinny_kernel<NMAX, R><<<items, 32 * wpc, 0, st>>>(xl, xu, w, d, yl, yu);
+    inf_bound_skinny_kernel<NMAX, R><<<items, 32 * wpc, 0, st>>>(xl, xu, w, d, yl, yu, post);
     return launch_status();
 }
 
@@ -195,19 +196,20 @@ bool skinny_ok(const Dims& d, const void* a, const void* b, const void* c) {
            aligned16(a) && aligned16(b) && (c == nullptr || aligned16(c));
 }
 
-int inf_forward_skinny(const float* x, const float* w, const Dims& d, float* y, int* pos, cudaStream_t st) {
-    if (d.COg <= 4) return launch_fwd<4, 4>(x, w, d, y, pos, st);
-    if (d.COg <= 8) return launch_fwd<8, 2>(x, w, d, y, pos, st);
-    if (d.COg <= 16) return launch_fwd<16, 2>(x, w, d, y, pos, st);
-    return launch_fwd<32, 1>(x, w, d, y, pos, st);
+int inf_forward_skinny(const float* x, const float* w, const Dims& d, float* y, int* pos, cudaStream_t st,
+                       const Post& post) {
+    if (d.COg <= 4) return launch_fwd<4, 4>(x, w, d, y, pos, st, post);
+    if (d.COg <= 8) return launch_fwd<8, 2>(x, w, d, y, pos, st, post);
+    if (d.COg <= 16) return launch_fwd<16, 2>(x, w, d, y, pos, st, post);
+    return launch_fwd<32, 1>(x, w, d, y, pos, st, post);
 }
 
 int inf_bound_skinny(const float* xl, const float* xu, const float* w, const Dims& d, float* yl, float* yu,
-                     cudaStream_t st) {
-    if (d.COg <= 4) return launch_bound<4, 4>(xl, xu, w, d, yl, yu, st);
-    if (d.COg <= 8) return launch_bound<8, 2>(xl, xu, w, d, yl, yu, st);
-    if (d.COg <= 16) return launch_bound<16, 2>(xl, xu, w, d, yl, yu, st);
-    return launch_bound<32, 1>(xl, xu, w, d, yl, yu, st);
+                     cudaStream_t st, const Post& post) {
+    if (d.COg <= 4) return launch_bound<4, 4>(xl, xu, w, d, yl, yu, st, post);
+    if (d.COg <= 8) return launch_bound<8, 2>(xl, xu, w, d, yl, yu, st, post);
+    if (d.COg <= 16) return launch_bound<16, 2>(xl, xu, w, d, yl, yu, st, post);
+    return launch_bound<32, 1>(xl, xu, w, d, yl, yu, st, post);
 }
 
 }  // namespace linf

@@ -48,9 +48,8 @@ class MLP(nn.Module):
         t = (_flat(x), _flat(lower), _flat(upper))
         for layer in self.fc:
             t = layer(*t)
-        y, lo, up = self.fc_last(*t)
-        neg = lambda v: None if v is None else -v
-        return [neg(y), neg(up), neg(lo)]
+        # negated layer: the value changes sign, the bounds change sign and places (model/mlp.py:22)
+        return list(self.fc_last(*t, negate=True))
 
 
 class Model(nn.Module):

@@ -190,14 +190,47 @@ def norm_dist(input, weight, group, p, use_custom_cuda_func=True, tag=None):
     return DistF.apply(input, weight, group, p, tag)
 
 
-def inf_dist_bound(input_lower, input_upper, weight, group, use_custom_cuda_func=True, tag=None):
-    """Interval bounds of an inf-dist layer; returns (output_lower, output_upper), no gradient."""
+def _post_args(post):
+    """(sub, add, negate) -> the three C arguments; vectors must be contiguous fp32 CUDA tensors or None."""
+    sub, add, negate = post if post is not None else (None, None, False)
+    for v, name in ((sub, "sub"), (add, "add")):
+        if v is not None:
+            _require(v, name)
+    return (sub.data_ptr() if sub is not None else None, add.data_ptr() if add is not None else None, 1 if negate else 0)
+
+
+@torch.no_grad()
+def inf_dist_post(input, weight, group, post, tag=None):
+    """Value of an inf-dist layer with the per-channel epilogue (sub, add, negate) folded into the
+    kernel's store: ((y - sub[c]) + add[c]), negated if asked.  No arg-max is kept, so there is no
+    gradient: the inference / certification path.  input [B, CI, HW], weight [CO, CI/group]."""
+    lib = _lib.load()
+    _require(input, "input"); _require(weight, "weight")
+    assert weight.size(1) * group == input.size(1)
+    B, CO, CI, G, HW = _shape5(input, weight, group)
+    y = torch.empty(B, CO, HW, device=input.device, dtype=torch.float32)
+    sub, add, neg = _post_args(post)
+    with torch.cuda.device(input.device):
+        need = lib.linf_inf_dist_forward_workspace_bytes(B, CO, CI, G, HW)
+        ws = _workspace(input.device, need) if need else None
+        rc = lib.linf_inf_dist_forward_post(input.data_ptr(), weight.data_ptr(), B, CO, CI, G, HW, sub, add, neg,
+                                            y.data_ptr(), ws.data_ptr() if need else None, ws.numel() if need else 0, _stream())
+    _lib.check(rc, "inf_dist_forward_post")
+    return y
+
+
+def inf_dist_bound(input_lower, input_upper, weight, group, use_custom_cuda_func=True, tag=None, post=None):
+    """Interval bounds of an inf-dist layer; returns (output_lower, output_upper), no gradient.
+    post = (sub, add, negate) folds the per-channel epilogue into the kernel (see inf_dist_post); with
+    negate the two outputs are also exchanged, so that lower <= upper still holds."""
     if not use_custom_cuda_func:
         _no_torch_branch()
     lib = _lib.load()
     _require(input_lower, "input_lower"); _require(input_upper, "input_upper"); _require(weight, "weight")
     assert weight.size(1) * group == input_lower.size(1) and input_upper.shape == input_lower.shape
     rows = _dense_route(input_lower, weight, group)
+    if rows and post is not None:
+        raise RuntimeError("the fused epilogue is available for dense layers (one spatial position) only")
     shape = (input_lower.size(0), input_lower.size(2))
     if rows:
         input_lower, input_upper = _rows_view(input_lower), _rows_view(input_upper)
@@ -205,12 +238,59 @@ def inf_dist_bound(input_lower, input_upper, weight, group, use_custom_cuda_func
     lo = torch.empty(B, CO, HW, device=input_lower.device, dtype=torch.float32)
     up = torch.empty_like(lo)
     with torch.cuda.device(input_lower.device):
-        rc = lib.linf_inf_dist_bound_forward(input_lower.data_ptr(), input_upper.data_ptr(), weight.data_ptr(),
-                                             B, CO, CI, G, HW, lo.data_ptr(), up.data_ptr(), _stream())
+        if post is None:
+            rc = lib.linf_inf_dist_bound_forward(input_lower.data_ptr(), input_upper.data_ptr(), weight.data_ptr(),
+                                                 B, CO, CI, G, HW, lo.data_ptr(), up.data_ptr(), _stream())
+        else:
+            sub, add, neg = _post_args(post)
+            rc = lib.linf_inf_dist_bound_forward_post(input_lower.data_ptr(), input_upper.data_ptr(), weight.data_ptr(),
+                                                      B, CO, CI, G, HW, sub, add, neg, lo.data_ptr(), up.data_ptr(), _stream())
     _lib.check(rc, "inf_dist_bound_forward")
     if rows:
         return _from_rows(lo, *shape), _from_rows(up, *shape)
     return lo, up
+
+
+class MeanShiftF(torch.autograd.Function):
+    """x[B, C] -> x - column mean(x), with the exponential running mean updated in the same launch
+    (csrc/epilogue.cu).  The backward is the same map applied to the gradient."""
+
+    @staticmethod
+    def forward(ctx, x, running_mean, momentum):
+        lib = _lib.load()
+        _require(x, "input")
+        out = torch.empty_like(x)
+        with torch.cuda.device(x.device):
+            rc = lib.linf_mean_shift(x.data_ptr(), x.size(0), x.size(1),
+                                     running_mean.data_ptr() if running_mean is not None else None,
+                                     float(momentum), out.data_ptr(), None, _stream())
+        _lib.check(rc, "mean_shift")
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        lib = _lib.load()
+        g = grad_output.contiguous()
+        out = torch.empty_like(g)
+        with torch.cuda.device(g.device):
+            rc = lib.linf_mean_shift(g.data_ptr(), g.size(0), g.size(1), None, 0.0, out.data_ptr(), None, _stream())
+        _lib.check(rc, "mean_shift backward")
+        return out, None, None
+
+
+_fused_mean_shift = True
+
+
+def set_fused_epilogue(flag):
+    """True (default): on CUDA, dense layers run the training-mode mean shift as one launch and fold the
+    eval-mode mean shift / bias / sign flip into the forward and bound kernels.  False: the same steps as
+    separate torch operations (the reference's sequence)."""
+    global _fused_mean_shift
+    _fused_mean_shift = bool(flag)
+
+
+def get_fused_epilogue():
+    return _fused_mean_shift
 
 
 class MeanNorm(nn.Module):
@@ -224,6 +304,10 @@ class MeanNorm(nn.Module):
         self.register_buffer("running_mean", torch.zeros(out_channels))
 
     def forward(self, x):
+        if (self.training and _fused_mean_shift and x.is_cuda and x.dtype == torch.float32
+                and x.numel() == x.size(0) * x.size(1) and x.numel() > 0 and self.running_mean.is_contiguous()):
+            # dense activation: mean, running mean and subtraction in one launch
+            return MeanShiftF.apply(x.reshape(x.size(0), x.size(1)).contiguous(), self.running_mean, self.momentum).view_as(x)
         flat = x.reshape(x.size(0), x.size(1), -1)
         if self.training:
             mean = flat.mean(dim=-1).mean(dim=0) if x.dim() > 2 else x.mean(dim=0)
@@ -275,19 +359,46 @@ class NormDistConv(nn.Module):
             t = t + self.bias.view(1, -1, 1, 1)
         return t
 
-    def forward(self, x, lower=None, upper=None):
+    def _fused_post(self, negate):
+        """(sub, add, negate) of this layer in eval mode, or None when the fused epilogue does not apply."""
+        if not _fused_mean_shift or self.training or not math.isinf(self.p) or not self.weight.is_cuda:
+            return None
+        sub = self.normalize.running_mean if self.normalize is not None else None
+        add = self.bias.detach() if self.bias is not None else None
+        if sub is None and add is None and not negate:
+            return None
+        return (sub, add, negate)
+
+    def forward(self, x, lower=None, upper=None, negate=False):
+        """negate=True returns the negated layer (value negated, bounds negated and exchanged): the
+        classifier layer of the distance nets, where a small distance means "this class"."""
         h, w = x.size(2), x.size(3)
         ho = (h + 2 * self.padding - self.dilation * (self.kernel_size - 1) - 1) // self.stride + 1
         wo = (w + 2 * self.padding - self.dilation * (self.kernel_size - 1) - 1) // self.stride + 1
         weight = self.weight.view(self.weight.size(0), -1)
         cols = self._patches(x)
-        y = norm_dist(cols, weight, self.group, p=self.p, tag=self.tag).view(x.size(0), -1, ho, wo)
-        y = self._post(y)
+        post = self._fused_post(negate)
+        if post is not None and _dense_route(cols, weight, self.group):
+            post = None
+        needs_grad = torch.is_grad_enabled() and (cols.requires_grad or weight.requires_grad)
+        if post is not None and not needs_grad:
+            # inference: mean shift, bias and sign flip leave the forward kernel already applied
+            y = inf_dist_post(cols.contiguous(), weight.detach(), self.group, post, tag=self.tag).view(x.size(0), -1, ho, wo)
+        else:
+            y = norm_dist(cols, weight, self.group, p=self.p, tag=self.tag).view(x.size(0), -1, ho, wo)
+            y = self._post(y)
+            if negate:
+                y = -y
         if lower is None or upper is None:
             return y, None, None
         assert math.isinf(self.p) and not self.training
+        if post is not None:
+            lo, up = inf_dist_bound(self._patches(lower).contiguous(), self._patches(upper).contiguous(), weight.detach(),
+                                    self.group, tag=self.tag, post=post)
+            return y, lo.view_as(y), up.view_as(y)
         lo, up = inf_dist_bound(self._patches(lower), self._patches(upper), weight, self.group, tag=self.tag)
-        return y, self._post(lo.view_as(y)), self._post(up.view_as(y))
+        lo, up = self._post(lo.view_as(y)), self._post(up.view_as(y))
+        return (y, -up, -lo) if negate else (y, lo, up)
 
     def extra_repr(self):
         s = f"{self.in_channels}, {self.out_channels}, kernel_size={self.kernel_size}, stride={self.stride}"
@@ -309,9 +420,9 @@ class NormDist(NormDistConv):
         super().__init__(in_features, out_features, 1, p=p, bias=bias, mean_normalize=mean_normalize,
                          identity_init=identity_init)
 
-    def forward(self, x, lower=None, upper=None):
+    def forward(self, x, lower=None, upper=None, negate=False):
         as4d = lambda t: None if t is None else t.reshape(t.size(0), t.size(1), 1, 1)
-        y, lo, up = super().forward(as4d(x), as4d(lower), as4d(upper))
+        y, lo, up = super().forward(as4d(x), as4d(lower), as4d(upper), negate=negate)
         flat = lambda t: None if t is None else t.reshape(t.size(0), t.size(1))
         return flat(y), flat(lo), flat(up)
 

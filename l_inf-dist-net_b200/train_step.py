@@ -75,7 +75,7 @@ class DataParallelStep:
     averaged gradient before its next use); only the order of launches differs.  With one rank
     there is no communication and the same schedule overlaps the optimiser with the passes."""
 
-    def __init__(self, net, optimizer, eager_bytes=None):
+    def __init__(self, net, optimizer, eager_bytes=None, urgent_group=True):
         import torch.distributed as dist
         self.net, self.opt = net, optimizer
         self.dist = dist if (dist.is_available() and dist.is_initialized()) else None
@@ -86,11 +86,31 @@ class DataParallelStep:
         self.eager_bytes = eager_bytes
         self.params = [p for p in net.parameters() if p.requires_grad]      # forward (registration) order
         self.first = self.params[0]
+        # The gradient of the FIRST layer is ready last and needed first: on the communicator that carries
+        # the other layers' all-reduces it would wait behind all of them, and the next forward behind it.
+        # It therefore travels on a communicator of its own (every rank issues the collectives of both
+        # communicators in the same order, the order of the backward pass), sharing the links with
+        # whatever is still in flight instead of queueing.
+        self.urgent = None
+        if self.world > 1 and self.cuda and urgent_group and self.avg is not None:
+            opts = self.dist.ProcessGroupNCCL.Options()
+            opts.is_high_priority_stream = True
+            self.urgent = self.dist.new_group(backend="nccl", pg_options=opts)
         if self.world > 1:
             for p in net.parameters():
                 self.dist.broadcast(p.data, src=0)
-        self.buffers = list(net.buffers()) if self.world > 1 else []
+        # the MeanNorm running means of all layers as views of ONE tensor: one broadcast per step
+        self.buffers, self.flat_buffers, self.buffer_work = [], None, None
+        if self.world > 1:
+            self.buffers = [b for b in net.buffers() if b.dtype == torch.float32]
+            if self.buffers:
+                self.flat_buffers = torch.cat([b.detach().reshape(-1) for b in self.buffers])
+                off = 0
+                for b in self.buffers:
+                    b.data = self.flat_buffers[off:off + b.numel()].view_as(b)
+                    off += b.numel()
         self.events = {}
+        self.trace = None               # set to a list to record, per waiting layer, how long the forward stalled
         self.sent, self.held = 0, []
         self.handles = [p.register_post_accumulate_grad_hook(self._on_grad) for p in self.params]
         if self.cuda:
@@ -102,10 +122,17 @@ class DataParallelStep:
     def _make_wait(self, own):
         def wait(module, inputs):
             cur = torch.cuda.current_stream()
+            marks = None
+            if self.trace is not None:
+                marks = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                marks[0].record(cur)
             for q in own:
                 ev = self.events.get(id(q))
                 if ev is not None:
                     cur.wait_event(ev)
+            if marks is not None:
+                marks[1].record(cur)
+                self.trace.append((type(module).__name__ + str(tuple(own[0].shape)), marks))
         return wait
 
     def _issue(self, p):
@@ -118,7 +145,8 @@ class DataParallelStep:
             return
         work = None
         if self.world > 1:
-            work = self.dist.all_reduce(p.grad, op=self.avg, async_op=True)
+            group = self.urgent if (p is self.first and self.urgent is not None) else None
+            work = self.dist.all_reduce(p.grad, op=self.avg, group=group, async_op=True)
         else:
             self.side.wait_stream(torch.cuda.current_stream())
         p.grad.record_stream(self.side)
@@ -146,10 +174,24 @@ class DataParallelStep:
             self.held.append(p)
 
     def __call__(self, *a, **k):
-        for b in self.buffers:
-            self.dist.broadcast(b, src=0, async_op=self.cuda)
+        # Rank 0's running means reach every replica BEFORE the forward touches them (the forward updates
+        # them in place).  The broadcast for step t + 1 is queued right after the forward of step t (nothing
+        # changes the running means in between), so that it has long landed when step t + 1 begins; the
+        # compute stream waits for it there (a stream-side wait, the host does not block).
+        if self.flat_buffers is not None:
+            if self.buffer_work is None:
+                self.buffer_work = self.dist.broadcast(self.flat_buffers, src=0, async_op=self.cuda)
+            if self.cuda:
+                self.buffer_work.wait()
+            self.buffer_work = None
         self.sent = 0
-        return self.net(*a, **k)
+        out = self.net(*a, **k)
+        if self.flat_buffers is not None and self.net.training:
+            if self.cuda:
+                # the collective runs on the communicator's stream: it must see this forward's updates
+                self.flat_buffers.record_stream(torch.cuda.current_stream())
+            self.buffer_work = self.dist.broadcast(self.flat_buffers, src=0, async_op=self.cuda)
+        return out
 
     def finish_step(self):
         """Call after loss.backward().  Parameters whose gradient never arrived through the hook of
@@ -165,6 +207,9 @@ class DataParallelStep:
 
     def close(self):
         """Takes the hooks off the network (the hooks hold this object, the object holds the network)."""
+        if self.buffer_work is not None and self.cuda:
+            self.buffer_work.wait()
+        self.buffer_work = None
         for h in self.handles:
             h.remove()
         self.handles = []
@@ -215,147 +260,6 @@ class ShardedNcclStep(DataParallelStep):
             ev.record(self.side)
 
 
-class ShardedCopyEngineStep(DataParallelStep):
-    """Data-parallel step for one replica per GPU on an NVLink/NVSwitch node in which the gradient
-    exchange of the large weight matrices uses no SM at all:
-
-      * every large parameter (rows divisible by the world size) lives in symmetric memory, so that
-        peers can write into it; rank r owns rows [r*s, (r+1)*s) of it together with the Adam moments
-        of those rows only (the optimiser state and work are sharded, the row-wise l_p decay makes
-        rows the natural unit);
-      * when the gradient of such a parameter is ready, rank r PUSHES chunk j of it into a staging
-        area on rank j with peer-to-peer copies (copy engines over NVLink) and then raises a flag in
-        rank j's memory with a stream memory operation; rank r waits -- again with stream memory
-        operations, not kernels -- for the W-1 chunks addressed to it, adds the W chunks in rank
-        order, divides by W, runs the fused optimiser kernel on its rows and pushes the updated rows
-        into every peer's copy of the parameter, raising a second flag;
-      * the next forward waits, layer by layer, for its own update and the W-1 flags of that layer.
-
-    Why not NCCL here: the forward kernels of the wide layers fill every SM for hundreds of
-    microseconds per CTA, so a collective kernel launched while they run starts only when they
-    end; with all-reduce kernels the exchange of the layers that finish their backward last ends up
-    exposed (6.3 ms per step on 8 GPUs against 5.0 ms on one).  Copies and flag operations need no
-    SM and run under the forward pass.  Small parameters (biases) keep the NCCL all-reduce of the
-    base class.  Every shard is reduced by exactly one rank in a fixed order and then copied, so all
-    replicas hold bit-identical parameters.
-
-    A rank that dies leaves its peers waiting on a flag (as a dead rank leaves NCCL waiting): run it
-    under a job-level timeout."""
-
-    MIN_BYTES = 1 << 20
-
-    def __init__(self, net, optimizer):
-        import torch.distributed as dist
-        import ctypes
-        import torch.distributed._symmetric_memory as symm_mem
-        super().__init__(net, optimizer)
-        if not (self.cuda and self.world > 1):
-            raise RuntimeError("ShardedCopyEngineStep needs CUDA tensors and more than one rank")
-        self.lib = _lib.load()
-        self.rank = dist.get_rank()
-        self.copy = torch.cuda.Stream()      # gradient chunks to their owners
-        self.push = torch.cuda.Stream()      # updated rows to every replica
-        group = dist.group.WORLD.group_name
-        W, r = self.world, self.rank
-        self.big = {}
-        for p in self.params:
-            if p.dim() < 2 or p.size(0) % W or p.numel() * 4 < self.MIN_BYTES:
-                continue
-            rows, cols = p.size(0), p.numel() // p.size(0)
-            s = rows // W
-            store = symm_mem.empty(p.numel(), dtype=torch.float32, device=p.device)
-            stage = symm_mem.empty(p.numel(), dtype=torch.float32, device=p.device)      # [W][s * cols]
-            flags = symm_mem.empty(2 * W, dtype=torch.int32, device=p.device)
-            flags.zero_()
-            store.copy_(p.data.reshape(-1))
-            hs, hg, hf = (symm_mem.rendezvous(t, group) for t in (store, stage, flags))
-            p.data = store.view(p.shape)
-            self.big[id(p)] = {
-                "rows": rows, "cols": cols, "s": s, "step": 0, "others": [(r + k) % W for k in range(1, W)],
-                "store": store.view(rows, cols), "stage": stage.view(W, s * cols), "flags": flags,
-                "peer_store": [hs.get_buffer(j, (rows, cols), torch.float32) for j in range(W)],
-                "peer_stage": [hg.get_buffer(j, (W, s * cols), torch.float32) for j in range(W)],
-                "peer_flags": [hf.get_buffer(j, (2 * W,), torch.int32) for j in range(W)],
-                "reduced": torch.empty(s, cols, dtype=torch.float32, device=p.device),
-                "updated": torch.cuda.Event(), "pushed": torch.cuda.Event(),
-            }
-            b = self.big[id(p)]
-            chunk = s * cols * 4
-            b["chunk_bytes"] = chunk
-            b["bytes"] = (ctypes.c_size_t * (W - 1))(*([chunk] * (W - 1)))
-            # gradient chunk r lands in slot r of the owner's staging area; its flag is word r there
-            b["d_rs"] = self._ptrs([b["peer_stage"][j][r].data_ptr() for j in b["others"]])
-            b["f_rs"] = self._ptrs([b["peer_flags"][j].data_ptr() + 4 * r for j in b["others"]])
-            b["f_wait"] = self._ptrs([flags.data_ptr() + 4 * j for j in b["others"]])
-            # updated rows of this rank into every replica; flag word W + r there
-            b["s_ag"] = self._ptrs([b["store"][r * s:(r + 1) * s].data_ptr()] * (W - 1))
-            b["d_ag"] = self._ptrs([b["peer_store"][j][r * s:(r + 1) * s].data_ptr() for j in b["others"]])
-            b["f_ag"] = self._ptrs([b["peer_flags"][j].data_ptr() + 4 * (W + r) for j in b["others"]])
-            b["f_fwd"] = self._ptrs([flags.data_ptr() + 4 * (W + j) for j in b["others"]])
-        torch.cuda.synchronize()
-        dist.barrier()
-
-    # ---- grouped peer copies and flag operations: one call into the library per group (no kernel,
-    # no SM; csrc/peer_push.cu) ----
-    @staticmethod
-    def _ptrs(values):
-        import ctypes
-        return (ctypes.c_void_p * len(values))(*values)
-
-    def _make_wait(self, own):
-        base = super()._make_wait(own)
-
-        def wait(module, inputs):
-            base(module, inputs)
-            cur = torch.cuda.current_stream()
-            for q in own:
-                b = self.big.get(id(q))
-                if b is not None and b["step"] > 0:
-                    cur.wait_event(b["updated"])
-                    _lib.check(self.lib.linf_flags_wait(self.world - 1, b["f_fwd"], b["step"], cur.cuda_stream), "flags_wait")
-        return wait
-
-    def _issue(self, p):
-        b = self.big.get(id(p))
-        if b is None:
-            return super()._issue(p)
-        W, r, s, cols = self.world, self.rank, b["s"], b["cols"]
-        n = W - 1
-        b["step"] += 1
-        t = b["step"]
-        grad = p.grad.view(W, s * cols)
-        ready = torch.cuda.Event()
-        ready.record(torch.cuda.current_stream())
-        p.grad.record_stream(self.copy)
-        p.grad.record_stream(self.side)
-        # 1. chunks of this rank's gradient to their owners, then the "chunk from r has landed" flags
-        self.copy.wait_event(ready)
-        g0 = p.grad.data_ptr()
-        src = self._ptrs([g0 + j * b["chunk_bytes"] for j in b["others"]])
-        _lib.check(self.lib.linf_peer_push(n, b["d_rs"], src, b["bytes"], n, b["f_rs"], t, self.copy.cuda_stream), "peer_push")
-        # 2. own shard: wait for the W-1 chunks, add in rank order, average, update the rows
-        with torch.cuda.stream(self.side):
-            self.side.wait_event(ready)
-            if t > 1:
-                self.side.wait_event(b["pushed"])     # last step's pushes have read the rows about to change
-            b["stage"][r].copy_(grad[r], non_blocking=True)
-            _lib.check(self.lib.linf_flags_wait(n, b["f_wait"], t, self.side.cuda_stream), "flags_wait")
-            torch.sum(b["stage"].view(W, s, cols), dim=0, out=b["reduced"])
-            b["reduced"].mul_(1.0 / W)
-            self.opt.step_rows(p, r * s, s, b["reduced"])
-            b["updated"].record(self.side)
-        # 3. the updated rows to every replica, on a stream of their own so that the next
-        #    parameter's reduction does not queue behind these copies
-        self.push.wait_event(b["updated"])
-        _lib.check(self.lib.linf_peer_push(n, b["d_ag"], b["s_ag"], b["bytes"], n, b["f_ag"], t, self.push.cuda_stream), "peer_push")
-        b["pushed"].record(self.push)
-
-    def synchronize(self):
-        super().synchronize()
-        torch.cuda.current_stream().wait_stream(self.copy)
-        torch.cuda.current_stream().wait_stream(self.push)
-
-
 def bench_train_step(device, world, rank, steps=8, warmup=3, batch=None, p=float("inf"), config="cifar"):
     """Times `steps` optimisation steps (after `warmup`), inputs copied from pinned host memory
     every step.  Returns a dict with samples/s over all ranks (max step time over ranks).
@@ -378,23 +282,16 @@ def bench_train_step(device, world, rank, steps=8, warmup=3, batch=None, p=float
         side, classes = 64, 200
         what = ("MLPFeature 12288-5120x5 + head 5120-512(tanh)-200, MeanNorm, eps 1/255, cross entropy, "
                 "fused AdamW lr .04 wd 5e-3")
-    exchange = "one NCCL all-reduce (avg) per parameter issued as its gradient is ready, optimiser applied per parameter as it arrives"
+    exchange = ("LINF_EXCHANGE=allreduce: one NCCL all-reduce (avg) per parameter issued as its gradient is ready (the first layer's on a "
+                "communicator of its own, so that it does not queue behind the others), fused optimiser per parameter as it arrives")
     model = None
     if world > 1 and device.type == "cuda":
         import os
         kind = os.environ.get("LINF_EXCHANGE", "allreduce")
         if kind == "sharded":
             model = ShardedNcclStep(net, opt)
-            exchange = ("per weight matrix a NCCL reduce-scatter (avg) as its gradient is ready, the fused optimiser on this "
+            exchange = ("LINF_EXCHANGE=sharded: per weight matrix a NCCL reduce-scatter (avg) as its gradient is ready, the fused optimiser on this "
                         "rank's rows only, a NCCL all-gather of the updated rows; biases by all-reduce")
-        elif kind == "copy":
-            try:
-                model = ShardedCopyEngineStep(net, opt)
-                exchange = ("weight gradients pushed shard by shard over NVLink by the copy engines, flags by stream memory "
-                            "operations, optimiser sharded by rows, updated rows pushed back (no SM used by the exchange); "
-                            "biases by NCCL all-reduce")
-            except Exception as exc:                   # no symmetric memory on this system: NCCL path
-                exchange += " (copy-engine exchange unavailable: %r)" % (exc,)
     if model is None:
         model = DataParallelStep(net, opt)
     gen = torch.Generator().manual_seed(4040 + rank)
@@ -404,8 +301,7 @@ def bench_train_step(device, world, rank, steps=8, warmup=3, batch=None, p=float
 
     # Every step copies its batch from pinned host memory; the copy of the NEXT batch is issued on a
     # stream of its own at the start of a step, so that it runs under this step's kernels instead of
-    # in front of the first layer (with the copy-engine exchange it would otherwise also queue behind
-    # the last parameter pushes of the previous step).
+    # in front of the first layer.
     h2d = torch.cuda.Stream() if device.type == "cuda" else None
     nxt = {}
 
@@ -440,21 +336,48 @@ def bench_train_step(device, world, rank, steps=8, warmup=3, batch=None, p=float
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
-    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
+    # one event per step boundary: the step time is the MEDIAN over the timed steps (a step ends when its
+    # last kernel on the compute stream has run; the optimiser updates it issued are waited for by the
+    # next step's layers, so over many steps nothing is left out)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    marks[0].record()
+    for k in range(steps):
         loss = step()
-    model.synchronize()
-    e1.record()
+        if k == steps - 1:
+            model.synchronize()
+        marks[k + 1].record()
     last = float(loss.item())
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / steps
+    per_step = sorted(marks[k].elapsed_time(marks[k + 1]) for k in range(steps))
+    ms = per_step[len(per_step) // 2]
+    ms_mean = marks[0].elapsed_time(marks[steps]) / steps
     if world > 1:
-        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        t = torch.tensor([ms, ms_mean], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+        ms, ms_mean = float(t[0].item()), float(t[1].item())
+    # How long the forward stood still waiting for updated weights (gradient exchange + optimiser not yet
+    # done when the layer was due): a few extra steps with an event pair around every layer's wait.
+    stalls = None
+    if isinstance(model, DataParallelStep) and device.type == "cuda":
+        model.trace = []
+        n_trace = 5
+        for _ in range(n_trace):
+            step()
+        model.synchronize()
+        torch.cuda.synchronize()
+        per_layer = {}
+        for name, (a, b) in model.trace:
+            per_layer[name] = per_layer.get(name, 0.0) + a.elapsed_time(b) / n_trace
+        model.trace = None
+        stalls = {"ms_per_step": sum(per_layer.values()), "per_layer_ms": per_layer,
+                  "what": "time the compute stream waited at each layer for that layer's updated weights (all-reduce + optimiser), "
+                          "mean of %d extra steps after the timed ones" % n_trace}
+        if world > 1:
+            t = torch.tensor([stalls["ms_per_step"]], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            stalls["ms_per_step_max_over_ranks"] = float(t.item())
     params = sum(q.numel() for q in net.parameters())
     # give the memory of this leg back before the next one (another model in the same process)
     model.close()
@@ -465,7 +388,9 @@ def bench_train_step(device, world, rank, steps=8, warmup=3, batch=None, p=float
         torch.cuda.empty_cache()
     name = "CIFAR-shape L_inf-dist net" if config == "cifar" else "TinyImageNet-shape L_inf-dist net+MLP"
     return {"metric": name + " train samples/s", "value": world * batch / (ms * 1e-3),
-            "unit": "samples/s", "ms_per_step": ms, "steps": steps, "batch_per_gpu": batch, "n_gpus": world,
-            "p": "inf" if math.isinf(p) else p, "loss": last, "parameters": params,
+            "unit": "samples/s", "ms_per_step": ms, "ms_per_step_mean": ms_mean, "steps": steps, "warmup": warmup,
+            "timing": "median over the timed steps, CUDA events, max over ranks",
+            "batch_per_gpu": batch, "n_gpus": world, "exchange": exchange if world > 1 else "none (one GPU)",
+            "p": "inf" if math.isinf(p) else p, "loss": last, "parameters": params, "forward_stall": stalls,
             "config": what + "; "
                       "n_gpus > 1: data parallel, " + exchange + "; backward mode as --backward"}

@@ -2,7 +2,7 @@
 
 Run in a container that has the reference checkout (it is not needed to run the tests):
 
-    python tests/golden/make_golden.py [--reference <checkout of zbh2047/L_inf-dist-net>]
+    python tests/golden/make_golden.py --reference <checkout of zbh2047/L_inf-dist-net>
 
 The script imports the reference's model/norm_dist.py (after registering an empty stand-in
 for its CUDA extension `norm_dist_cpp`, which that file imports unconditionally) and calls its
@@ -48,7 +48,8 @@ def load_reference(path):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("LINF_REFERENCE"), required=os.environ.get("LINF_REFERENCE") is None,
+                    help="checkout of zbh2047/L_inf-dist-net (or set LINF_REFERENCE)")
     args = ap.parse_args()
     ref = load_reference(args.reference)
     torch.set_num_threads(1)

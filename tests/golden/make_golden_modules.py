@@ -18,6 +18,8 @@ Everything is computed by the reference's own Python on the CPU:
                        call norm_dist with the CUDA branch as default, so the script binds
                        use_custom_cuda_func=False).  The layer width unit (model/mlp.py: net_width)
                        is set to 64 so that the fixture stays small; weights are plain N(0,1) draws.
+                       For the p = inf runs also the certification pass of main.py:166-194 on the
+                       state after the two steps (eval mode, bounds through every layer, margins).
 The reference file model/norm_dist.py imports its CUDA extension unconditionally; an empty stand-in
 module named norm_dist_cpp is registered first.
 """
@@ -177,6 +179,16 @@ def make_small_nets(ref_adamw, bm, mlp, model, nd, out):
                 opt.step()
             for k, v in net.state_dict().items():
                 out[f"{tag}_sd2_{k}"] = v.numpy().copy()
+            if pname == "inf":
+                # certification pass of main.py:166-194 on the trained state: eval mode, clamped eps box,
+                # bounds through every layer, worst-case margins
+                net.eval()
+                eps = 8 / 255 if kind == "mlp" else 1 / 255
+                with torch.no_grad():
+                    lower = torch.max(x - eps, torch.zeros(())); upper = torch.min(x + eps, torch.ones(()))
+                    outputs, margins = net(x, lower=lower, upper=upper, targets=targets)
+                out[f"{tag}_cert_outputs"] = outputs.numpy().copy()
+                out[f"{tag}_cert_margins"] = margins.numpy().copy()
 
 
 def main():

@@ -126,8 +126,26 @@ def assert_bits_equal(a, b, what):
 # is measured against the largest entry of the tensor: |a - b| <= LP_RTOL * max|b| (floor=1).
 # For scale: the reference's own fp32 PyTorch branch sits 6e-7 (p=8), 1e-6 (p=16), 3.5e-6 (p=64)
 # from double precision under this measure, and up to 2e-4 on individual small entries.
+# Two more measures are REPORTED for every gradient comparison (and collected in LP_REPORT): the
+# mixed one, |a - b| / max(|b|, 1e-2 * max|b|), and the plain elementwise one over the entries
+# with |b| >= 1e-3 * max|b|.
 LP_RTOL = 1e-5
 LP_FLOOR = 1.0
+LP_REPORT = []
+
+
+def lp_errors(a, b):
+    """(normwise, mixed with floor 1e-2, elementwise over entries >= 1e-3 of the largest) relative errors."""
+    a = a.detach().cpu().numpy() if torch.is_tensor(a) else np.asarray(a)
+    b = b.detach().cpu().numpy() if torch.is_tensor(b) else np.asarray(b)
+    a = a.astype(np.float64); b = b.astype(np.float64)
+    if b.size == 0:
+        return 0.0, 0.0, 0.0
+    top = max(float(np.abs(b).max()), 1e-300)
+    err = np.abs(a - b)
+    big = np.abs(b) >= 1e-3 * top
+    return (float(err.max() / top), float((err / np.maximum(np.abs(b), 1e-2 * top)).max()),
+            float((err[big] / np.abs(b[big])).max()) if big.any() else 0.0)
 
 
 def assert_lp_close(a, b, what, floor=LP_FLOOR, rtol=LP_RTOL):
@@ -137,5 +155,8 @@ def assert_lp_close(a, b, what, floor=LP_FLOOR, rtol=LP_RTOL):
     scale = np.maximum(np.abs(b), floor * np.abs(b).max())
     err = np.abs(a - b) / np.maximum(scale, 1e-300)
     worst = float(err.max()) if err.size else 0.0
+    norm, mixed, elem = lp_errors(a, b)
+    LP_REPORT.append((what, norm, mixed, elem))
+    print(f"[lp] {what}: normwise {norm:.2e}, mixed(floor 1e-2) {mixed:.2e}, elementwise(|b| >= 1e-3 max) {elem:.2e}")
     assert worst <= rtol, f"{what}: max scaled error {worst:.3e} > {rtol}"
     return worst

@@ -219,6 +219,76 @@ def test_lp_config2_slice_and_annealing_points(cuda, lib):
 REF_LIB = os.path.join(ROOT, "oracle", "_ref", "libref_norm_dist.so")
 
 
+def _ref_lib():
+    return ctypes.CDLL(REF_LIB) if os.path.exists(REF_LIB) else None
+
+
+@pytest.mark.parametrize("p", [8.0, 16.0, 64.0])
+def test_lp_config2_full_size(cuda, lib, p):
+    """B = 512, Din = Dout = 5120 (x, w, grad_out ~ N(0,1)) at full size on the GPU.  The double-precision
+    checker is run on samples that keep it cheap and still cover every reduction at its full length:
+    forward and grad_input on 8 batch rows (they depend on that row only), grad_weight on 8 output channels
+    (they depend on that channel over all 512 rows).  The whole forward is also compared with the
+    reference's own CUDA kernel."""
+    B, CI, CO = 512, 5120, 5120
+    x, w, g = make_inputs(B, CI, CO, 1, 1, seed=2021, x_dist="normal")
+    xd, wd, gd = dev(x), dev(w), dev(g)
+    y = c_lp_forward(xd, wd, 1, p)
+    gx, gw = c_lp_backward(gd, xd, wd, y, 1, p)
+    torch.cuda.synchronize()
+    yh = y.cpu().numpy()
+    rng = np.random.default_rng(int(p))
+    rows = np.sort(rng.choice(B, 8, replace=False)); cols = np.sort(rng.choice(CO, 8, replace=False))
+    y_rows = oracle.norm_dist_forward(x[rows], w, 1, p)
+    assert_lp_close(yh[rows], y_rows, f"forward rows p={p}", floor=0.0)
+    # gradients from the GPU's own fp32 output, so that only the backward arithmetic is compared
+    gx_rows, _ = oracle.norm_dist_backward(g[rows], x[rows], w, yh[rows], 1, p)
+    assert_lp_close(gx.cpu().numpy()[rows], gx_rows, f"grad_input rows p={p}")
+    _, gw_cols = oracle.norm_dist_backward(np.ascontiguousarray(g[:, cols]), x, np.ascontiguousarray(w[cols]),
+                                           np.ascontiguousarray(yh[:, cols]), 1, p)
+    assert_lp_close(gw.cpu().numpy()[cols], gw_cols, f"grad_weight channels p={p}")
+    ref = _ref_lib()
+    if ref is not None:
+        P = lambda t: ctypes.c_void_p(t.data_ptr())
+        y_r = torch.empty_like(y)
+        ref.ref_norm_dist_forward(P(xd), P(wd), B, CO, CI, 1, 1, P(y_r), ctypes.c_float(p))
+        torch.cuda.synchronize()
+        torch.testing.assert_close(y, y_r, rtol=2e-5, atol=0)
+
+
+@pytest.mark.parametrize("G", [1, 4])
+def test_inf_bound_config3_full_size(cuda, lib, G):
+    """B = 512, Din = 3072, Dout = 5120 (x ~ U[0,1), box of 8/255 clamped to [0,1]), groups 1 and 4: lower and
+    upper bit-exact against the reference's own CUDA kernel over the whole output, and against the CPU
+    checker on 8 sampled batch rows."""
+    B, CI, CO = 512, 3072, 5120
+    x, w, _ = make_inputs(B, CI, CO, 1, G, seed=2022)
+    eps = np.float32(8.0 / 255.0)
+    lo = np.clip(x - eps, 0, 1).astype(np.float32); up = np.clip(x + eps, 0, 1).astype(np.float32)
+    lod, upd, wd = dev(lo), dev(up), dev(w)
+    yl, yu = c_inf_bound(lod, upd, wd, G)
+    torch.cuda.synchronize()
+    rows = np.sort(np.random.default_rng(G).choice(B, 8, replace=False))
+    yl_rows, yu_rows = oracle.inf_dist_bound(lo[rows], up[rows], w, G)
+    assert_bits_equal(yl.cpu().numpy()[rows], yl_rows, "lower rows"); assert_bits_equal(yu.cpu().numpy()[rows], yu_rows, "upper rows")
+    ref = _ref_lib()
+    if ref is not None:
+        P = lambda t: ctypes.c_void_p(t.data_ptr())
+        yl_r = torch.empty_like(yl); yu_r = torch.empty_like(yu)
+        ref.ref_inf_dist_bound_forward(P(lod), P(upd), P(wd), B, CO, CI, G, 1, P(yl_r), P(yu_r))
+        torch.cuda.synchronize()
+        assert_bits_equal(yl, yl_r, "lower vs reference kernel"); assert_bits_equal(yu, yu_r, "upper vs reference kernel")
+    # the value path at the same shape: forward + arg-max against the reference kernel and the sampled rows
+    y, pos = c_inf_forward(dev(x), wd, G)
+    y_rows, pos_rows = oracle.inf_dist_forward(x[rows], w, G)
+    assert_bits_equal(y.cpu().numpy()[rows], y_rows, "values rows"); assert_bits_equal(pos.cpu().numpy()[rows], pos_rows, "arg-max rows")
+    if ref is not None:
+        y_r = torch.empty_like(y); pos_r = torch.empty_like(pos)
+        ref.ref_inf_dist_forward(P(dev(x)), P(wd), B, CO, CI, G, 1, P(y_r), P(pos_r))
+        torch.cuda.synchronize()
+        assert_bits_equal(y, y_r, "values vs reference kernel"); assert_bits_equal(pos, pos_r, "arg-max vs reference kernel")
+
+
 @pytest.mark.skipif(not os.path.exists(REF_LIB), reason="reference kernels were not prebuilt")
 @pytest.mark.parametrize("shape", [(33, 100, 65, 1, 1), (130, 784, 200, 1, 1), (16, 64, 256, 1, 4),
                                    (3, 18, 12, 5, 3), (512, 784, 5120, 1, 1)], ids=_ids)
@@ -250,14 +320,13 @@ def test_against_reference_kernels(cuda, lib, shape):
     gx, gw = c_inf_backward(gd, pos, CI, G, "ordered")
     torch.testing.assert_close(gx, gx_r, rtol=1e-4, atol=2e-4); torch.testing.assert_close(gw, gw_r, rtol=1e-4, atol=2e-4)
     # finite p: both sides approximate; the reference uses lg2/ex2 approximations
-    if B * CI * CO <= 10 ** 8:
-        xn = dev(make_inputs(B, CI, CO, HW, G, seed=41, x_dist="normal")[0])
-        for p in (8.0, 16.0):
-            yp_r = torch.empty_like(y_r)
-            ref.ref_norm_dist_forward(P(xn), P(wd), B, CO, CI, G, HW, P(yp_r), ctypes.c_float(p))
-            torch.cuda.synchronize()
-            yp = c_lp_forward(xn, wd, G, p)
-            torch.testing.assert_close(yp, yp_r, rtol=2e-5, atol=0)
+    xn = dev(make_inputs(B, CI, CO, HW, G, seed=41, x_dist="normal")[0])
+    for p in (8.0, 16.0):
+        yp_r = torch.empty_like(y_r)
+        ref.ref_norm_dist_forward(P(xn), P(wd), B, CO, CI, G, HW, P(yp_r), ctypes.c_float(p))
+        torch.cuda.synchronize()
+        yp = c_lp_forward(xn, wd, G, p)
+        torch.testing.assert_close(yp, yp_r, rtol=2e-5, atol=0)
 
 
 @pytest.mark.parametrize("p_norm", [float("inf"), 8.0, 23.7, None])
@@ -374,7 +443,7 @@ def test_norm_dist_conv_module(cuda, lib):
 def test_faster_than_reference_kernels(cuda, lib):
     """Config-1 layer (B=512, Din=784, Dout=5120): forward + backward of this library against the
     reference's own CUDA kernels compiled for sm_100a, same inputs, CUDA events, L2 flushed.  The
-    measured times are written to gpurun_out/ref_gpu_timing.json (when that folder can be made)."""
+    measured times are written to ref_gpu_timing.json in the folder LINF_REPORT_DIR names, if set."""
     import json
     from linfdist_b200 import _lib
     from helpers import stream
@@ -541,25 +610,170 @@ def test_adamw_step_rows_equals_whole_tensor_step(cuda, lib):
     assert torch.equal(whole.weight.data, parts.weight.data)
 
 
-def test_peer_push_and_flags_on_one_gpu(cuda, lib):
-    """The grouped copy + flag helpers of the copy-engine exchange, exercised inside one GPU: copies
-    land, flags are written behind them, and a wait on flags that already hold the value returns."""
-    import ctypes
-    src = torch.arange(3 * 1000, dtype=torch.float32, device="cuda").view(3, 1000)
-    dst = torch.zeros(3, 1000, device="cuda")
-    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+def test_certify_config4_shape_bit_exact(cuda, lib):
+    """The certification pass (eval mode, clamped eps box, five distance layers 3072-5120x4-10 with their
+    eval-mode mean shift / bias, margins) on the GPU against the CPU checker chained layer by layer."""
+    import linfdist_b200 as L
+    from linfdist_b200.train_step import build_cifar_net
+    B, eps = 48, 8.0 / 255.0
+    net = build_cifar_net(torch.device("cuda:0"))
+    gen = torch.Generator().manual_seed(77)
+    for m in net.modules():
+        if isinstance(m, L.MeanNorm):
+            m.running_mean.copy_(torch.randn(m.running_mean.shape, generator=gen).cuda() + 9.0)
+    net.feature.fc_last.bias.data = torch.randn(10, generator=gen).cuda()
+    x = torch.rand(B, 3, 32, 32, generator=gen); t = torch.randint(0, 10, (B,), generator=gen)
+    ok, margins = L.certify(net, x.cuda(), t.cuda(), eps, torch.ones((), device="cuda"), torch.zeros((), device="cuda"))
+    lo = torch.max(x - eps, torch.zeros(())).reshape(B, -1).numpy(); up = torch.min(x + eps, torch.ones(())).reshape(B, -1).numpy()
+    layers = list(net.feature.fc) + [net.feature.fc_last]
+    for layer in layers:
+        w = layer.weight.detach().view(layer.weight.size(0), -1).cpu().numpy()
+        lo, up = oracle.inf_dist_bound(lo[:, :, None], up[:, :, None], w, 1)
+        lo, up = lo[:, :, 0], up[:, :, 0]
+        if layer.normalize is not None:
+            rm = layer.normalize.running_mean.cpu().numpy()
+            lo, up = lo - rm, up - rm
+        if layer.bias is not None:
+            b = layer.bias.detach().cpu().numpy()
+            lo, up = lo + b, up + b
+    lo, up = -up, -lo                                         # a small distance means "this class"
+    tn = t.numpy()
+    ref = up - lo[np.arange(B), tn][:, None]
+    ref[np.arange(B), tn] = 0.0
+    assert_bits_equal(margins, ref.astype(np.float32), "worst-case margins")
+    assert np.array_equal(ok.cpu().numpy(), ref.argmax(axis=1) == tn)
+
+
+def test_pgd_runs_the_input_gradient_only(cuda, lib):
+    """AttackPGD freezes the parameters, so the backward of every distance layer produces grad_input
+    alone; that gradient must be the one a full backward gives, and one step of `find` must be the
+    sign step projected onto the eps ball and the data range."""
+    import torch.nn.functional as F
+    import linfdist_b200 as L
+    torch.manual_seed(1)
+    net = L.Model(L.MLP(3, 1, (3, 8, 8), num_classes=10), L.BoundFinalIdentity(), eps=8 / 255).cuda()
+    L.set_p_norm(net, float("inf"))
+    net.eval()
+    x = torch.rand(32, 3, 8, 8, device="cuda"); t = torch.randint(0, 10, (32,), device="cuda")
+    xa = x.clone().requires_grad_(True)
+    F.cross_entropy(net(xa), t, reduction="sum").backward()
+    assert all(q.grad is not None for q in net.parameters())
+    full = xa.grad.clone()
+    net.zero_grad(set_to_none=True)
+    eps, step = 8 / 255, 2 / 255
+    up, down = torch.ones((), device="cuda"), torch.zeros((), device="cuda")
+    adv = L.AttackPGD(net, eps, step, 1, up, down, random_start=False).find(x, t)
+    assert all(q.grad is None for q in net.parameters()) and all(q.requires_grad for q in net.parameters())
+    want = torch.min(torch.max(torch.min(torch.max(x + step * torch.sign(full), x - eps), x + eps), down), up)
+    assert torch.equal(adv, want)
+    adv = L.AttackPGD(net, eps, step, 5, up, down, random_start=True).find(x, t)
+    assert float((adv - x).abs().max()) <= eps + 1e-6 and float(adv.min()) >= 0 and float(adv.max()) <= 1
+
+
+@pytest.mark.parametrize("shape", [(512, 5120), (7, 33), (64, 100), (513, 31)])
+def test_mean_shift_one_launch(cuda, lib, shape):
+    """Training-mode mean shift in one launch: the mean agrees with torch's reduction to fp32 rounding (the
+    summation order differs), and GIVEN that mean the subtraction and the running-mean update are the
+    torch sequence of model/norm_dist.py:85-97 bit for bit.  Its backward is the same map on the gradient."""
+    import linfdist_b200 as L
+    from helpers import stream
+    rows, cols = shape
+    gen = torch.Generator().manual_seed(rows + cols)
+    x = (torch.randn(rows, cols, generator=gen) * 3 + 10).cuda()
+    rm0 = torch.randn(cols, generator=gen).cuda()
+    rm = rm0.clone(); out = torch.empty_like(x); mean = torch.empty(cols, device="cuda")
+    assert lib.linf_mean_shift(x.data_ptr(), rows, cols, rm.data_ptr(), 0.1, out.data_ptr(), mean.data_ptr(), stream()) == 0
     torch.cuda.synchronize()
-    ptrs = lambda v: (ctypes.c_void_p * len(v))(*v)
-    s = torch.cuda.Stream()
-    rc = lib.linf_peer_push(3, ptrs([dst[i].data_ptr() for i in range(3)]), ptrs([src[i].data_ptr() for i in range(3)]),
-                            (ctypes.c_size_t * 3)(4000, 4000, 4000), 2, ptrs([flags.data_ptr() + 4, flags.data_ptr() + 20]),
-                            7, s.cuda_stream)
-    assert rc == 0
-    s.synchronize()
-    assert torch.equal(dst, src) and flags.tolist() == [0, 7, 0, 0, 0, 7, 0, 0]
-    # only now, with the value known to be there, queue a wait for it (and for an older value)
-    assert lib.linf_flags_wait(2, ptrs([flags.data_ptr() + 4, flags.data_ptr() + 20]), 7, s.cuda_stream) == 0
-    assert lib.linf_flags_wait(1, ptrs([flags.data_ptr() + 4]), 3, s.cuda_stream) == 0
-    s.synchronize()
-    assert lib.linf_peer_push(0, None, None, None, 65, ptrs([flags.data_ptr()] * 65), 1, s.cuda_stream) == 2   # too many flags
-    assert lib.linf_flags_wait(1, ptrs([flags.data_ptr() + 2]), 1, s.cuda_stream) == 6                          # misaligned word
+    exact = x.double().mean(dim=0)
+    assert float((mean.double() - exact).abs().max()) <= 2e-6 * float(x.abs().max())
+    assert float((mean - x.mean(dim=0)).abs().max()) <= 4e-6 * float(x.abs().max())
+    assert torch.equal(out, x - mean)
+    assert torch.equal(rm, rm0.clone().mul_(1 - 0.1).add_(mean, alpha=0.1))
+    # in place, and without a running mean
+    y = x.clone()
+    assert lib.linf_mean_shift(y.data_ptr(), rows, cols, None, 0.0, y.data_ptr(), None, stream()) == 0
+    assert torch.equal(y, out)
+    # the module: fused and torch paths agree to rounding, forward and backward
+    m_f, m_t = L.MeanNorm(cols).cuda(), L.MeanNorm(cols).cuda()
+    xa = x.clone().requires_grad_(True); xb = x.clone().requires_grad_(True)
+    g = torch.randn(rows, cols, generator=gen).cuda()
+    ya = m_f(xa); ya.backward(g)
+    L.set_fused_epilogue(False)
+    try:
+        yb = m_t(xb); yb.backward(g)
+    finally:
+        L.set_fused_epilogue(True)
+    torch.testing.assert_close(ya, yb, rtol=0, atol=4e-6 * float(x.abs().max()))
+    torch.testing.assert_close(xa.grad, xb.grad, rtol=0, atol=4e-6 * float(g.abs().max()))
+    torch.testing.assert_close(m_f.running_mean, m_t.running_mean, rtol=0, atol=1e-6 * float(x.abs().max()))
+
+
+@pytest.mark.parametrize("case", [(64, 784, 5120, True, False, False), (37, 5120, 10, False, True, True), (130, 100, 65, True, True, False),
+                                  (9, 18, 7, True, True, True), (512, 3072, 640, True, False, False), (33, 256, 96, False, False, True)],
+                         ids=lambda c: "B{}_CI{}_CO{}_mn{}_bias{}_neg{}".format(*[int(v) for v in c]))
+def test_eval_epilogue_in_kernel_bit_exact(cuda, lib, case):
+    """Eval mode: mean shift by the running mean, bias and sign flip applied inside the forward and bound
+    kernels (tiled, few-output and generic paths) against the same steps as separate torch operations
+    (model/norm_dist.py:137-140, :150-155, model/mlp.py:22): identical bits for value, lower and upper."""
+    import linfdist_b200 as L
+    B, CI, CO, mean_normalize, bias, negate = case
+    torch.manual_seed(CI + CO)
+    layer = L.NormDist(CI, CO, bias=bias, mean_normalize=mean_normalize).cuda()
+    L.set_p_norm(layer, float("inf"))
+    if mean_normalize:
+        layer.normalize.running_mean.copy_(torch.randn(CO).cuda() + 5)
+    if bias:
+        layer.bias.data = torch.randn(CO).cuda()
+    layer.eval()
+    x = torch.rand(B, CI, device="cuda"); lo = (x - 0.02).clamp(0, 1); up = (x + 0.02).clamp(0, 1)
+    with torch.no_grad():
+        fused = layer(x, lo, up, negate=negate)
+        L.set_fused_epilogue(False)
+        try:
+            plain = layer(x, lo, up, negate=negate)
+        finally:
+            L.set_fused_epilogue(True)
+    for a, b, name in zip(fused, plain, ("value", "lower", "upper")):
+        assert_bits_equal(a, b, name)
+    assert bool((fused[1] <= fused[2]).all())
+    # with gradients required the value takes the arg-max path and the torch steps: same numbers
+    xg = x.clone().requires_grad_(True)
+    yg, _, _ = layer(xg, negate=negate)
+    assert_bits_equal(yg.detach(), fused[0], "value with autograd")
+    yg.sum().backward()
+    assert xg.grad is not None
+
+
+def test_training_step_with_and_without_fused_mean_shift(cuda, lib):
+    """Two optimisation steps of a small net with the one-launch mean shift and with the torch sequence:
+    the same parameters up to the rounding of the batch means."""
+    import linfdist_b200 as L
+    from linfdist_b200.train_step import MarginLoss, hinge
+
+    def run(fused):
+        L.set_fused_epilogue(fused)
+        torch.manual_seed(3)
+        net = L.Model(L.MLP(3, 1, (3, 8, 8), num_classes=10), L.BoundFinalIdentity(), eps=8 / 255).cuda()
+        for m in net.modules():
+            if isinstance(m, L.NormDist):
+                m.weight.data.normal_()
+        L.set_p_norm(net, 8.0)
+        opt = L.AdamW(net, lr=0.02, betas=(0.9, 0.99), eps=1e-3, weight_decay=5e-3)
+        loss_fn = MarginLoss(hinge(0.75), 1.0)
+        gen = torch.Generator().manual_seed(5)
+        for _ in range(2):
+            x = torch.rand(64, 3, 8, 8, generator=gen).cuda(); t = torch.randint(0, 10, (64,), generator=gen).cuda()
+            out, worst = net(x, targets=t)
+            loss = loss_fn(out, worst, t)
+            opt.zero_grad(set_to_none=True)
+            loss.backward()
+            opt.step()
+        torch.cuda.synchronize()
+        return [q.detach().clone() for q in net.parameters()] + [b.clone() for b in net.buffers()]
+
+    try:
+        a, b = run(True), run(False)
+    finally:
+        L.set_fused_epilogue(True)
+    for qa, qb in zip(a, b):
+        torch.testing.assert_close(qa, qb, rtol=1e-4, atol=1e-5)

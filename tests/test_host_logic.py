@@ -229,8 +229,11 @@ def _ddp_worker(rank, world, port, out, overlapped):
     flat = torch.cat([p.detach().flatten() for p in net.parameters()])
     gathered = [torch.zeros_like(flat) for _ in range(world)]
     dist.all_gather(gathered, flat)
+    bufs = torch.cat([b.detach().flatten() for b in net.buffers()])
+    all_bufs = [torch.zeros_like(bufs) for _ in range(world)]
+    dist.all_gather(all_bufs, bufs)
     if rank == 0:
-        out.put((bool(all(torch.equal(gathered[0], g) for g in gathered)), gathered[0]))
+        out.put((bool(all(torch.equal(gathered[0], g) for g in gathered)), gathered[0].numpy().copy(), torch.stack(all_bufs).numpy().copy()))   # plain arrays: the process may exit before the parent reads
     dist.destroy_process_group()
 
 
@@ -242,20 +245,28 @@ def _run_two_ranks(overlapped):
     procs = [ctx.Process(target=_ddp_worker, args=(r, 2, port, out, overlapped)) for r in range(2)]
     for p in procs:
         p.start()
-    same, params = out.get(timeout=240)
+    same, params, bufs = out.get(timeout=240)
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
     assert same is True
-    return params
+    return torch.from_numpy(params), torch.from_numpy(bufs)
 
 
 def test_data_parallel_two_ranks_gloo():
     """Two CPU ranks, different batch shards: parameters stay identical across ranks, and applying
     the optimiser parameter by parameter inside backward gives what a plain DDP step gives."""
-    plain = _run_two_ranks(False)
-    overlapped = _run_two_ranks(True)
+    plain, plain_bufs = _run_two_ranks(False)
+    overlapped, over_bufs = _run_two_ranks(True)
     assert torch.allclose(plain, overlapped, rtol=1e-6, atol=1e-7)
+    # MeanNorm running means: every step starts from rank 0's values and adds the rank's own batch
+    # statistics.  DistributedDataParallel broadcasts rank 0's buffers at the start of the NEXT forward, so its
+    # ranks end a step with different values; the hand-scheduled step sends them right after the forward
+    # (they are then in place long before the next step needs them), so every replica ends the step with
+    # rank 0's values -- the values DDP's rank 0 holds, and the ones every rank would start the next step from.
+    assert not torch.equal(plain_bufs[0], plain_bufs[1])
+    assert torch.allclose(plain_bufs[0], over_bufs[0], rtol=1e-6, atol=1e-7)
+    assert torch.equal(over_bufs[0], over_bufs[1])
 
 
 def test_bench_sharding_inputs():

@@ -185,8 +185,52 @@ def test_small_net_steps_match_reference(device, kind, pname, p, request, monkey
             # distance first) therefore ends up to 2 * lr apart, and drags the next step's batch means along.
             # Such cells must stay a vanishing fraction; all others agree to rounding.
             off = err > 1e-4
-            limit = 0.15 if "running_mean" in k else 5e-3
+            # (a channel's batch mean moves with ANY entry of its weight row: half of the means may show it)
+            limit = 0.5 if "running_mean" in k else 5e-3
             assert off.double().mean() <= limit, f"{k}: {int(off.sum())} of {off.numel()} entries differ by more than 1e-4"
             assert float(err.max()) <= (5e-3 if "running_mean" in k else 5 * HYPER["lr"]), (k, float(err.max()))
         else:
             assert float(err.max()) <= 1e-4, (k, float(err.max()))
+
+
+# ---------------------------------------------------------------------------------------------
+# certification pass (main.py:166-194)
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("kind", ["mlp", "feat"])
+def test_certify_matches_reference(device, kind, request, monkeypatch):
+    """certify() on the reference's trained small net: bounds through every distance layer (fused
+    lower/upper kernel), eval-mode mean shift, bias, final margins.  The distance layers are exact
+    (max / min of exactly rounded differences), so for the pure distance net the margins must be
+    the reference's bit for bit; the dense head of the other net is a GEMM in another order."""
+    import linfdist_b200.nets as nets
+    monkeypatch.setattr(nets, "UNIT", 64)
+    if device == "cuda":
+        request.getfixturevalue("cuda"); request.getfixturevalue("lib")
+    else:
+        import cpu_ops
+        cpu_ops.patch(monkeypatch)
+    z = np.load(os.path.join(GOLDEN, "small_nets.npz"))
+    tag = f"{kind}_inf"
+    classes = 10 if kind == "mlp" else 20
+    eps = 8 / 255 if kind == "mlp" else 1 / 255
+    if kind == "mlp":
+        net = L.Model(L.MLP(3, 1, (3, 8, 8), num_classes=classes), L.BoundFinalIdentity(), eps=0.5)
+    else:
+        net = L.Model(L.MLPFeature(2, 1, (3, 8, 8)), L.Predictor(64, 32, classes), eps=0.5)
+    net.load_state_dict({k[len(tag) + 5:]: T(z[k], "cpu") for k in z.files if k.startswith(tag + "_sd2_")}, strict=True)
+    net = net.to(device)
+    L.set_p_norm(net, 8.0)
+    net.train()
+    x = T(z["x"], device); targets = T(z[f"{kind}_targets"], device)
+    ok, margins = L.certify(net, x, targets, eps, torch.ones((), device=device), torch.zeros((), device=device))
+    assert net.training and L.get_p_norm(net) == 8.0 and L.get_eps(net) == 0.5      # state restored
+    ref = z[f"{tag}_cert_margins"]
+    if kind == "mlp":
+        assert np.array_equal(margins.cpu().numpy().view(np.uint32), ref.view(np.uint32))
+    else:
+        close(margins, ref, "margins", 2e-5, 2e-5)
+    assert torch.equal(ok.cpu(), torch.from_numpy(ref).max(dim=1)[1] == T(z[f"{kind}_targets"], "cpu"))
+    acc = L.certified_accuracy(net, [(x[:10], targets[:10]), (x[10:], targets[10:])], eps,
+                               torch.ones((), device=device), torch.zeros((), device=device))
+    assert abs(acc - float(ok.float().mean())) < 1e-6
