@@ -15,16 +15,18 @@ import torch
 import torch.nn.functional as F
 
 from .nets import get_eps, set_eps
-from .norm_dist import get_p_norm, set_p_norm
+from .norm_dist import bounds_only, get_p_norm, set_p_norm
 
 
 @torch.no_grad()
-def certify(net, inputs, targets, eps, up, down):
+def certify(net, inputs, targets, eps, up, down, values=False):
     """Worst-case margins of one batch under an l_inf perturbation of radius eps.
 
     up / down: tensors broadcastable to `inputs` with the largest / smallest valid input value per
     element (the normalised data range).  Returns (certified [B] bool, margins [B, classes]); the p
-    norm, eps and train/eval state of the net are restored."""
+    norm, eps and train/eval state of the net are restored.  The margins depend on the propagated bounds
+    alone, so by default the distance layers skip their value path (values=True runs it as the
+    reference's loop does: same margins, one more kernel per layer)."""
     save_p, save_eps, was_training = get_p_norm(net), get_eps(net), net.training
     set_eps(net, eps)
     set_p_norm(net, float("inf"))
@@ -32,7 +34,11 @@ def certify(net, inputs, targets, eps, up, down):
     try:
         lower = torch.max(inputs - eps, down)
         upper = torch.min(inputs + eps, up)
-        margins = net(inputs, lower=lower, upper=upper, targets=targets)[1]
+        if values:
+            margins = net(inputs, lower=lower, upper=upper, targets=targets)[1]
+        else:
+            with bounds_only():
+                margins = net(inputs, lower=lower, upper=upper, targets=targets)[1]
     finally:
         set_p_norm(net, save_p)
         set_eps(net, save_eps)
@@ -41,12 +47,12 @@ def certify(net, inputs, targets, eps, up, down):
 
 
 @torch.no_grad()
-def certified_accuracy(net, batches, eps, up, down):
+def certified_accuracy(net, batches, eps, up, down, values=False):
     """Fraction of samples certified over an iterable of (inputs, targets) batches already on the
     net's device (the reference moves each batch there itself, main.py:177-180)."""
     good = total = 0
     for inputs, targets in batches:
-        ok, _ = certify(net, inputs, targets, eps, up, down)
+        ok, _ = certify(net, inputs, targets, eps, up, down, values=values)
         good += int(ok.sum().item())
         total += targets.numel()
     return good / max(total, 1)

@@ -94,7 +94,7 @@ inf_forward_generic_kernel(const float* __restrict__ x, const float* __restrict_
 // =====================================================================================
 // Geometry of one kernel variant.  A thread owns 8 rows x TN columns; a warp (4 x 8 lanes)
 // owns 32 rows x 8*TN columns; a CTA has 2 warps along m and NT/64 along n.
-template <int NT_, int TN_, int BK_, int MINB_, int TW_ = BK_>
+template <int NT_, int TN_, int BK_, int MINB_, int TW_ = BK_, int PAD_ = 4, int STAGES_ = 0>
 struct Geo {
     static constexpr int NT = NT_, TN = TN_, BK = BK_, MINB = MINB_;
     static constexpr int TW = TW_;                      // terms per arg-max tracking window
@@ -102,8 +102,8 @@ struct Geo {
     static constexpr int BM = 64, BN = (NT / 64) * 8 * TN;
     static constexpr int NOUT = 8 * TN;                 // outputs per thread
     static constexpr int TILE_OUT = BM * BN;
-    static constexpr int LD = BK + 4;                   // padded row length in floats
-    static constexpr int STAGES = (BK <= 16) ? 4 : 3;
+    static constexpr int LD = BK + PAD_;                // row length in shared memory, in floats (PAD_ = 0: swizzled rows)
+    static constexpr int STAGES = STAGES_ > 0 ? STAGES_ : (BK <= 16) ? 4 : 3;
     static constexpr int STAGE_FLOATS = (BM + BN) * LD;
     static constexpr int SMEM_BYTES = STAGES * STAGE_FLOATS * 4;
     static_assert(BK % TW == 0 && TW % 4 == 0 && (NSUB == 1 || NSUB % 2 == 0), "tracking window");
@@ -177,19 +177,57 @@ __device__ __forceinline__ void load_stage(float* stage, const TiledParams& p, c
 
 // Columns [4*K4B, 4*K4E) of one k-tile of the (max, |a-b|) product for the 8 x TN sub-tile of this
 // thread.  `in` holds the running maxima before, `out` after (they may alias).
-template <class GEO, int K4B, int K4E>
-__device__ __forceinline__ void tile_step(const float* __restrict__ As, const float* __restrict__ Bs,
+// Where the fragments of a thread lie in a stage.  Padded rows (cp.async loader, first TMA loader):
+// row pitch LD = BK + 4 floats, chunk k4 of a row at k4 * 4.
+template <class GEO>
+struct FragPadded {
+    const float* As; const float* Bs;     // first row of the thread's x / w fragments
+    __device__ __forceinline__ ulonglong2 a(int i, int k4) const {
+        return *reinterpret_cast<const ulonglong2*>(As + (4 * i) * GEO::LD + k4 * 4);
+    }
+    __device__ __forceinline__ ulonglong2 b(int j, int k4) const {
+        return *reinterpret_cast<const ulonglong2*>(Bs + (8 * j) * GEO::LD + k4 * 4);
+    }
+};
+__device__ __forceinline__ ulonglong2 lds128(unsigned addr) {
+    ulonglong2 v;
+    asm volatile("ld.shared.v2.u64 {%0, %1}, [%2];" : "=l"(v.x), "=l"(v.y) : "r"(addr));
+    return v;
+}
+// Swizzled rows (TMA loader with the 128-byte swizzle; BK = 32, rows of exactly 128 bytes): the copy
+// engine stores 16-byte chunk c of row r at chunk position c ^ (r & 7).  The rows of a thread's x
+// fragments are r = (multiple of 32) + lm + 4 * i, so r & 7 = lm | ((i & 1) << 2); those of its w fragments
+// are r = (multiple of 8) + ln + 8 * j, so r & 7 = ln.  The run-time part of the exclusive-or is folded
+// into four (x) and eight (w) base pointers per k-tile; everything else is a compile-time offset.
+template <class GEO>
+struct FragSwizzled {
+    unsigned Aq[4], Bc[8];                 // shared-memory byte addresses
+    __device__ __forceinline__ void set(const float* As, const float* Bs, int lm, int ln) {
+        const unsigned a0 = (unsigned)__cvta_generic_to_shared(As), b0 = (unsigned)__cvta_generic_to_shared(Bs);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) Aq[q] = a0 + ((unsigned)(q ^ lm) << 4);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) Bc[c] = b0 + ((unsigned)(c ^ ln) << 4);
+    }
+    __device__ __forceinline__ ulonglong2 a(int i, int k4) const {
+        return lds128(Aq[k4 & 3] + (unsigned)((4 * i) * 128 + ((((k4 >> 2) ^ (i & 1)) & 1) << 6)));
+    }
+    __device__ __forceinline__ ulonglong2 b(int j, int k4) const { return lds128(Bc[k4] + (unsigned)((8 * j) * 128)); }
+};
+
+template <class GEO, int K4B, int K4E, class FRAG>
+__device__ __forceinline__ void tile_step(const FRAG& fr,
                                           const float (&in)[GEO::NOUT], float (&out)[GEO::NOUT]) {
-    constexpr int LD = GEO::LD, TN = GEO::TN;
+    constexpr int TN = GEO::TN;
 #pragma unroll
     for (int k4 = K4B; k4 < K4E; ++k4) {
         ulonglong2 bf[TN];
 #pragma unroll
         for (int j = 0; j < TN; ++j)
-            bf[j] = *reinterpret_cast<const ulonglong2*>(Bs + (8 * j) * LD + k4 * 4);
+            bf[j] = fr.b(j, k4);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            const ulonglong2 af = *reinterpret_cast<const ulonglong2*>(As + (4 * i) * LD + k4 * 4);
+            const ulonglong2 af = fr.a(i, k4);
 #pragma unroll
             for (int j = 0; j < TN; ++j) {
                 float a = (k4 == K4B) ? in[i * TN + j] : out[i * TN + j];
@@ -218,21 +256,21 @@ __device__ __forceinline__ void note_raises(const float (&before)[NOUT], const f
 
 // The NSUB tracking windows of one k-tile, ping-ponging between the two accumulator sets; NSUB is
 // even here, so the tile starts and ends in accA.
-template <class GEO, int S>
-__device__ __forceinline__ void tracked_windows(const float* __restrict__ As, const float* __restrict__ Bs,
+template <class GEO, int S, class FRAG>
+__device__ __forceinline__ void tracked_windows(const FRAG& fr,
                                                 float (&accA)[GEO::NOUT], float (&accB)[GEO::NOUT],
                                                 unsigned (&cid)[GEO::NOUT / 2], unsigned win0) {
     if constexpr (S < GEO::NSUB) {
         constexpr int K4B = S * GEO::TW / 4, K4E = (S + 1) * GEO::TW / 4;
         const unsigned dup = (win0 + S) * 0x10001u;
         if constexpr ((S & 1) == 0) {
-            tile_step<GEO, K4B, K4E>(As, Bs, accA, accB);
+            tile_step<GEO, K4B, K4E>(fr, accA, accB);
             note_raises<GEO::NOUT>(accA, accB, cid, dup);
         } else {
-            tile_step<GEO, K4B, K4E>(As, Bs, accB, accA);
+            tile_step<GEO, K4B, K4E>(fr, accB, accA);
             note_raises<GEO::NOUT>(accB, accA, cid, dup);
         }
-        tracked_windows<GEO, S + 1>(As, Bs, accA, accB, cid, win0);
+        tracked_windows<GEO, S + 1>(fr, accA, accB, cid, win0);
     }
 }
 
@@ -330,12 +368,14 @@ inf_forward_tiled_kernel(const __grid_constant__ TiledParams p) {
     __shared__ int s_last;
     __shared__ int s_dead;
     __shared__ __align__(8) unsigned long long s_full[STAGES];   // TMA loader: "stage filled" barriers
-    // TMA writes want a 128-byte aligned destination: the launcher reserves 128 bytes for the round-up
-    float* smem = LOADER == 1
-        ? reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t)127) : smem_raw;
+    // TMA writes want a 128-byte aligned destination, swizzled ones (LOADER == 2) a 1024-byte aligned one
+    // (the swizzle pattern repeats every eight 128-byte rows): the launcher reserves the bytes for the round-up
+    constexpr uintptr_t ALIGN = LOADER == 2 ? 1024 : 128;
+    float* smem = LOADER >= 1
+        ? reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(smem_raw) + ALIGN - 1) & ~(ALIGN - 1)) : smem_raw;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if constexpr (LOADER == 1) {
+    if constexpr (LOADER >= 1) {
         if (tid == 0) {
             s_dead = 0;
 #pragma unroll
@@ -383,7 +423,7 @@ inf_forward_tiled_kernel(const __grid_constant__ TiledParams p) {
         const StageSrc<GEO> src = stage_src<GEO>(p, g, m0, n0, tid);
         __syncthreads();   // previous segment is done with the ring
         int rd = 0, wr = STAGES - 1;
-        if constexpr (LOADER == 1) {
+        if constexpr (LOADER >= 1) {
             // the ring position carries over from segment to segment (the barriers' phases depend on it)
             rd = (int)(filled % STAGES); wr = (rd + STAGES - 1) % STAGES;
         }
@@ -425,7 +465,14 @@ inf_forward_tiled_kernel(const __grid_constant__ TiledParams p) {
                 next_stage(kt);
                 const float* As = smem + rd * STAGE_FLOATS + row_off * GEO::LD;
                 const float* Bs = smem + rd * STAGE_FLOATS + (BM + col_off) * GEO::LD;
-                tracked_windows<GEO, 0>(As, Bs, accA, accB, cid, (unsigned)(kt * NSUB));
+                if constexpr (LOADER == 2) {
+                    FragSwizzled<GEO> fr;
+                    fr.set(As, Bs, lm, ln);
+                    tracked_windows<GEO, 0>(fr, accA, accB, cid, (unsigned)(kt * NSUB));
+                } else {
+                    const FragPadded<GEO> fr{As, Bs};
+                    tracked_windows<GEO, 0>(fr, accA, accB, cid, (unsigned)(kt * NSUB));
+                }
                 advance();
             }
         } else {
@@ -438,16 +485,25 @@ inf_forward_tiled_kernel(const __grid_constant__ TiledParams p) {
                         next_stage(ktc);
                         const float* As = smem + rd * STAGE_FLOATS + row_off * GEO::LD;
                         const float* Bs = smem + rd * STAGE_FLOATS + (BM + col_off) * GEO::LD;
-                        if constexpr (TRACK) {
-                            if (h == 0) {
-                                tile_step<GEO, 0, BK / 4>(As, Bs, accA, accB);
-                                note_raises<NOUT>(accA, accB, cid, (unsigned)ktc * 0x10001u);
+                        auto body = [&](const auto& fr) {
+                            if constexpr (TRACK) {
+                                if (h == 0) {
+                                    tile_step<GEO, 0, BK / 4>(fr, accA, accB);
+                                    note_raises<NOUT>(accA, accB, cid, (unsigned)ktc * 0x10001u);
+                                } else {
+                                    tile_step<GEO, 0, BK / 4>(fr, accB, accA);
+                                    note_raises<NOUT>(accB, accA, cid, (unsigned)ktc * 0x10001u);
+                                }
                             } else {
-                                tile_step<GEO, 0, BK / 4>(As, Bs, accB, accA);
-                                note_raises<NOUT>(accB, accA, cid, (unsigned)ktc * 0x10001u);
+                                tile_step<GEO, 0, BK / 4>(fr, accA, accA);
                             }
+                        };
+                        if constexpr (LOADER == 2) {
+                            FragSwizzled<GEO> fr;
+                            fr.set(As, Bs, lm, ln);
+                            body(fr);
                         } else {
-                            tile_step<GEO, 0, BK / 4>(As, Bs, accA, accA);
+                            body(FragPadded<GEO>{As, Bs});
                         }
                         advance();
                     } else if (TRACK && h == 1) {
@@ -556,29 +612,33 @@ struct Kernels {
 struct Variant {
     Kernels main;      // 64 x 64 output tiles (8 x 4 outputs per thread), 3 CTAs per SM
     Kernels tail;      // 64 x 32 output tiles (8 x 2 outputs per thread) for a partial last wave
-    bool tma;
+    int tma;           // 0: cp.async loader; 1: TMA, padded boxes; 2: TMA, 128-byte swizzle
 };
 
 template <class GEO, int LOADER = 0>
 constexpr Kernels make_kernels() {
-    return Kernels{GEO::BM, GEO::BN, GEO::BK, GEO::NT, GEO::MINB, GEO::SMEM_BYTES + (LOADER == 1 ? 128 : 0),
+    return Kernels{GEO::BM, GEO::BN, GEO::BK, GEO::NT, GEO::MINB, GEO::SMEM_BYTES + (LOADER == 1 ? 128 : LOADER == 2 ? 1024 : 0),
                    inf_forward_tiled_kernel<GEO, true, LOADER>, inf_forward_tiled_kernel<GEO, false, LOADER>};
 }
 
-// All variants: CTAs of 128 threads.  Measured on B200, us per forward with arg-max at
-// B = 512, Dout = 5120 and Din = 784 / 1024 / 3072 / 5120 (whole tiles + tail launch below 1536, k-split above):
-//   0: 192 / 230 / 596 / 954      1: 190 / 237 / 620 / 997      2: 204 / 247 / 611 / 962
-// (the same kernels with the register budget of 4 CTAs per SM: 206-218 / 249-263 / 653-678 / 1022-1085).
+// All variants: CTAs of 128 threads, 8 x 4 outputs per thread, 3 CTAs per SM.  Measured on one B200, us per
+// forward with arg-max at B = 512, Dout = 5120 and Din = 784 / 1024 / 3072 / 5120 (whole tiles + tail launch
+// below 1536, k-split above), same box:
+//   0: 196 / 238 / 592 / 942      1: 202 / 242 / 606 / 965      (0 with 4 stages: 200 / 239 / 600 / 950)
+// and on another box   1: 192 / 230 / 596 / 954      2: 190 / 237 / 620 / 997      3: 204 / 247 / 611 / 962
+// (variants 1-3 with the register budget of 4 CTAs per SM: 206-218 / 249-263 / 653-678 / 1022-1085).
 const Variant kVariants[] = {
-    // 0: 32-term k-tiles (3 stages), 8-term tracking windows (default)
-    {make_kernels<Geo<128, 4, 32, 3, 8>>(), make_kernels<Geo<128, 2, 32, 4, 8>>(), false},
-    // 1: 16-term k-tiles (4 stages), 8-term tracking windows
-    {make_kernels<Geo<128, 4, 16, 3, 8>>(), make_kernels<Geo<128, 2, 16, 4, 8>>(), false},
-    // 2: 16-term k-tiles, one tracking window per k-tile
-    {make_kernels<Geo<128, 4, 16, 3, 16>>(), make_kernels<Geo<128, 2, 16, 4, 16>>(), false},
-    // 3: as 2 with the TMA loader (measured 7-14 % slower than 2: the extra four columns per row cost
-    //    L2 traffic and one thread issues every copy)
-    {make_kernels<Geo<128, 4, 16, 3, 16>, 1>(), make_kernels<Geo<128, 2, 16, 4, 16>>(), true},
+    // 0: 32-term k-tiles fetched by TMA with the 128-byte swizzle (unpadded rows, 3 stages), 8-term windows (default)
+    {make_kernels<Geo<128, 4, 32, 3, 8, 0>, 2>(), make_kernels<Geo<128, 2, 32, 4, 8>>(), 2},
+    // 1: 32-term k-tiles (cp.async, 3 stages), 8-term tracking windows
+    {make_kernels<Geo<128, 4, 32, 3, 8>>(), make_kernels<Geo<128, 2, 32, 4, 8>>(), 0},
+    // 2: 16-term k-tiles (cp.async, 4 stages), 8-term tracking windows
+    {make_kernels<Geo<128, 4, 16, 3, 8>>(), make_kernels<Geo<128, 2, 16, 4, 8>>(), 0},
+    // 3: 16-term k-tiles, one tracking window per k-tile
+    {make_kernels<Geo<128, 4, 16, 3, 16>>(), make_kernels<Geo<128, 2, 16, 4, 16>>(), 0},
+    // 4: as 3 with TMA and padded boxes (measured 7-14 % slower than 3: the extra four columns per row cost L2
+    //    traffic)
+    {make_kernels<Geo<128, 4, 16, 3, 16>, 1>(), make_kernels<Geo<128, 2, 16, 4, 16>>(), 1},
 };
 constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
 
@@ -659,7 +719,7 @@ static EncodeTiledFn tma_encoder() {
 // width a multiple of 16 bytes; the kernel only ever starts a box at a column that is a multiple
 // of 16 floats.
 static bool tma_matrix(const float* base, size_t rows, size_t cols, size_t pitch, int box_cols, int box_rows,
-                       CUtensorMap* out) {
+                       CUtensorMap* out, bool swizzle128 = false) {
     EncodeTiledFn fn = tma_encoder();
     if (fn == nullptr || (reinterpret_cast<uintptr_t>(base) & 15u) || (pitch & 3u) || (box_cols & 3)) return false;
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -667,13 +727,14 @@ static bool tma_matrix(const float* base, size_t rows, size_t cols, size_t pitch
     const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     const cuuint32_t elem[2] = {1, 1};
     return fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, elem,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // The TMA loader zero-fills past the END OF A ROW OF THE MATRIX.  With groups the k-tiles of one
 // group are followed by the next group's columns, so a ragged last k-tile is only right for G = 1.
-static bool tma_shape_ok(const Dims& d) { return (d.G == 1 || d.CIg % 16 == 0) && d.CIg >= 32 && d.R >= 1; }
+static bool tma_shape_ok(const Dims& d, int bk) { return (d.G == 1 || d.CIg % bk == 0) && d.CIg >= 32 && d.R >= 1; }
 
 static int launch_tiled(const Kernels& k, const TiledParams& p, bool track, cudaStream_t st) {
     auto kern = track ? k.track : k.plain;
@@ -723,10 +784,11 @@ int inf_forward(const float* x, const float* w, const Dims& d, float* y, int* po
         if (cudaMemsetAsync(p.tickets, 0, tick_bytes, st) != cudaSuccess) return LINF_ERR_LAUNCH;
     }
     if (v.tma) {
-        const bool ok = tma_shape_ok(d) &&
-                        tma_matrix(x, (size_t)d.R, (size_t)d.CI, (size_t)d.CI, use->bk + 4, use->bm, &p.tm_x) &&
-                        tma_matrix(w, (size_t)d.CO, (size_t)d.CIg, (size_t)d.CIg, use->bk + 4, use->bn, &p.tm_w);
-        if (!ok) use = &kVariants[2].main;      // same geometry with the cp.async loader
+        const int pad = v.tma == 1 ? 4 : 0;
+        const bool ok = tma_shape_ok(d, use->bk) &&
+                        tma_matrix(x, (size_t)d.R, (size_t)d.CI, (size_t)d.CI, use->bk + pad, use->bm, &p.tm_x, v.tma == 2) &&
+                        tma_matrix(w, (size_t)d.CO, (size_t)d.CIg, (size_t)d.CIg, use->bk + pad, use->bn, &p.tm_w, v.tma == 2);
+        if (!ok) use = &kVariants[v.tma == 1 ? 3 : 1].main;      // same geometry with the cp.async loader
     }
     // Whole tiles that end in a partial wave of CTAs (or never fill one): the columns of that
     // partial wave are run as tiles of half the width by the tail kernels, twice as many CTAs.

@@ -279,6 +279,21 @@ class MeanShiftF(torch.autograd.Function):
 
 
 _fused_mean_shift = True
+_bounds_only = False
+
+
+class bounds_only:
+    """Context manager: distance layers that are given lower / upper bounds in eval mode skip their value
+    path and return the lower bound in its place.  For passes that use the bounds alone (certification:
+    the worst-case margins never look at the value), saving one forward kernel per layer."""
+
+    def __enter__(self):
+        global _bounds_only
+        self.saved, _bounds_only = _bounds_only, True
+
+    def __exit__(self, *exc):
+        global _bounds_only
+        _bounds_only = self.saved
 
 
 def set_fused_epilogue(flag):
@@ -381,7 +396,9 @@ class NormDistConv(nn.Module):
         if post is not None and _dense_route(cols, weight, self.group):
             post = None
         needs_grad = torch.is_grad_enabled() and (cols.requires_grad or weight.requires_grad)
-        if post is not None and not needs_grad:
+        if _bounds_only and lower is not None and upper is not None and not self.training and not needs_grad:
+            y = None                     # filled with the lower bound below: nobody reads the value in such a pass
+        elif post is not None and not needs_grad:
             # inference: mean shift, bias and sign flip leave the forward kernel already applied
             y = inf_dist_post(cols.contiguous(), weight.detach(), self.group, post, tag=self.tag).view(x.size(0), -1, ho, wo)
         else:
@@ -392,13 +409,17 @@ class NormDistConv(nn.Module):
         if lower is None or upper is None:
             return y, None, None
         assert math.isinf(self.p) and not self.training
+        shape = (x.size(0), -1, ho, wo)
         if post is not None:
             lo, up = inf_dist_bound(self._patches(lower).contiguous(), self._patches(upper).contiguous(), weight.detach(),
                                     self.group, tag=self.tag, post=post)
-            return y, lo.view_as(y), up.view_as(y)
-        lo, up = inf_dist_bound(self._patches(lower), self._patches(upper), weight, self.group, tag=self.tag)
-        lo, up = self._post(lo.view_as(y)), self._post(up.view_as(y))
-        return (y, -up, -lo) if negate else (y, lo, up)
+            lo, up = lo.view(shape), up.view(shape)
+        else:
+            lo, up = inf_dist_bound(self._patches(lower), self._patches(upper), weight, self.group, tag=self.tag)
+            lo, up = self._post(lo.view(shape)), self._post(up.view(shape))
+            if negate:
+                lo, up = -up, -lo
+        return (lo if y is None else y), lo, up
 
     def extra_repr(self):
         s = f"{self.in_channels}, {self.out_channels}, kernel_size={self.kernel_size}, stride={self.stride}"

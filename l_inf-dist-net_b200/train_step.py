@@ -83,6 +83,7 @@ class DataParallelStep:
         self.avg = self.dist.ReduceOp.AVG if (self.dist and self.dist.get_backend() == "nccl") else None
         self.cuda = next(net.parameters()).is_cuda
         self.side = torch.cuda.Stream() if self.cuda else None
+        self.side_first = torch.cuda.Stream() if self.cuda else None     # optimiser of the first layer: see below
         self.eager_bytes = eager_bytes
         self.params = [p for p in net.parameters() if p.requires_grad]      # forward (registration) order
         self.first = self.params[0]
@@ -90,7 +91,8 @@ class DataParallelStep:
         # the other layers' all-reduces it would wait behind all of them, and the next forward behind it.
         # It therefore travels on a communicator of its own (every rank issues the collectives of both
         # communicators in the same order, the order of the backward pass), sharing the links with
-        # whatever is still in flight instead of queueing.
+        # whatever is still in flight instead of queueing, and its optimiser update runs on a stream of
+        # its own instead of behind the updates of the other layers (which wait for their all-reduces).
         self.urgent = None
         if self.world > 1 and self.cuda and urgent_group and self.avg is not None:
             opts = self.dist.ProcessGroupNCCL.Options()
@@ -144,20 +146,21 @@ class DataParallelStep:
             self.opt.step_params([p])
             return
         work = None
+        side = self.side_first if p is self.first else self.side
         if self.world > 1:
             group = self.urgent if (p is self.first and self.urgent is not None) else None
             work = self.dist.all_reduce(p.grad, op=self.avg, group=group, async_op=True)
         else:
-            self.side.wait_stream(torch.cuda.current_stream())
-        p.grad.record_stream(self.side)
-        with torch.cuda.stream(self.side):
+            side.wait_stream(torch.cuda.current_stream())
+        p.grad.record_stream(side)
+        with torch.cuda.stream(side):
             if work is not None:
                 work.wait()                       # stream-side wait: the host does not block
             self.opt.step_params([p])
             ev = self.events.get(id(p))
             if ev is None:
                 ev = self.events[id(p)] = torch.cuda.Event()
-            ev.record(self.side)
+            ev.record(side)
 
     def _on_grad(self, p):
         nbytes = p.grad.numel() * p.grad.element_size()
@@ -204,6 +207,7 @@ class DataParallelStep:
         """Makes the current stream wait for every update issued so far."""
         if self.cuda:
             torch.cuda.current_stream().wait_stream(self.side)
+            torch.cuda.current_stream().wait_stream(self.side_first)
 
     def close(self):
         """Takes the hooks off the network (the hooks hold this object, the object holds the network)."""

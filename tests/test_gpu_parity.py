@@ -80,6 +80,7 @@ def test_inf_forward_config1_full_size(cuda, lib):
         y, pos = c_inf_forward(dev(x), dev(w), 1, use_ws=use_ws)
         assert_bits_equal(y, y_ref, "values")
         assert_bits_equal(pos, pos_ref, "arg-max")
+    assert lib.linf_tune_set(2, 0) == 0          # no bounded wait of the TMA loader has ever run out
     gx_ref, gw_ref = oracle.inf_dist_backward(g, pos_ref, 784, 1)
     gx, gw = c_inf_backward(dev(g), dev(pos_ref), 784, 1, "ordered")
     assert_bits_equal(gx, gx_ref, "grad_input"); assert_bits_equal(gw, gw_ref, "grad_weight")
@@ -567,15 +568,17 @@ def test_inf_backward_synthetic_positions(cuda, lib, pattern, shape):
 
 @pytest.mark.parametrize("shape", [(64, 64, 64, 1, 1), (33, 100, 65, 1, 1), (130, 784, 200, 1, 1), (16, 64, 256, 1, 4),
                                    (70, 1000, 96, 1, 1), (512, 784, 640, 1, 1), (64, 3072, 512, 1, 4), (9, 36, 40, 1, 1)], ids=_ids)
-def test_inf_forward_tma_loader_variant(cuda, lib, shape):
-    """The same tiled kernel with its operand tiles fetched by TMA (tiled bulk copies, completion on
-    mbarriers) instead of cp.async: a build option that is not the default (it measured slower), kept
-    bit-identical.  Ragged k-tiles, rows and channels past the end arrive as zeros from the copy engine;
-    the bounded waits must never have run out."""
+@pytest.mark.parametrize("variant", [4, 1, 2, 3], ids=["tma_padded", "cp_async_32", "cp_async_16", "window_16"])
+def test_inf_forward_other_loader_variants(cuda, lib, shape, variant):
+    """The default forward fetches its operand tiles by TMA (tiled bulk copies with the 128-byte swizzle,
+    completion on mbarriers).  The other variants of the same kernel -- TMA with padded boxes, cp.async
+    with 32- or 16-term k-tiles, one tracking window per k-tile -- must give the same bits.  Ragged
+    k-tiles, rows and channels past the end arrive as zeros from the copy engine; the bounded waits
+    of the TMA loaders must never have run out."""
     B, CI, CO, HW, G = shape
     x, w, _ = make_inputs(B, CI, CO, HW, G, seed=77 + CI)
     y_ref, pos_ref = oracle.inf_dist_forward(x, w, G)
-    assert lib.linf_tune_set(0, 3) == 0
+    assert lib.linf_tune_set(0, variant) == 0
     try:
         for use_ws in (False, True):
             y, pos = c_inf_forward(dev(x), dev(w), G, use_ws=use_ws)
@@ -642,6 +645,15 @@ def test_certify_config4_shape_bit_exact(cuda, lib):
     ref[np.arange(B), tn] = 0.0
     assert_bits_equal(margins, ref.astype(np.float32), "worst-case margins")
     assert np.array_equal(ok.cpu().numpy(), ref.argmax(axis=1) == tn)
+    # with the value path run as well (the reference's loop), and with the torch epilogue: the same margins
+    _, m2 = L.certify(net, x.cuda(), t.cuda(), eps, torch.ones((), device="cuda"), torch.zeros((), device="cuda"), values=True)
+    assert_bits_equal(m2, margins, "margins with the value path")
+    L.set_fused_epilogue(False)
+    try:
+        _, m3 = L.certify(net, x.cuda(), t.cuda(), eps, torch.ones((), device="cuda"), torch.zeros((), device="cuda"), values=True)
+    finally:
+        L.set_fused_epilogue(True)
+    assert_bits_equal(m3, margins, "margins with separate elementwise passes")
 
 
 def test_pgd_runs_the_input_gradient_only(cuda, lib):
