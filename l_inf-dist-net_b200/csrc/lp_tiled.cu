@@ -285,7 +285,9 @@ lp_backward_tiled_kernel(const LpParams p) {
             const float* Gs = st + (wm * 32 + lm) * LDK;
             const float* Ys = st + GY + (wm * 32 + lm) * LDK;
             const float* Ws = st + 2 * GY + col_off;
-#pragma unroll
+            // not unrolled: the body of one k4 step is 128 power evaluations; four copies of it do not fit the
+            // instruction cache (the profile of the fully unrolled loop showed instruction fetch as its top stall)
+#pragma unroll 1
             for (int k4 = 0; k4 < BK / 4; ++k4) {
                 float4 wv[4];
 #pragma unroll
