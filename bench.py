@@ -323,20 +323,29 @@ def extra_legs(torch, lib, dev, flush, lane_peak, hbm_peak):
           "bound": "fp32-issue (integer p: the powers are multiplies on the FP32 pipe; no MUFU on this path)",
           "ops_per_term": "forward: subtract, scale by 1/M, log2(p) squarings, add; each gradient: subtract, scale by 1/y, "
                           "log2(p-2)+1 multiplies for s*|s|^(p-2), multiply by g, add"}
-    for p in (8.0, 16.0, 64.0):
+    import math
+    for p in (8.0, 16.0, 64.0, 11.3):
         a = (x.data_ptr(), w.data_ptr(), Bq, CO, CI, 1, 1)
         t_f = _timed_us(torch, lambda: _lib.check(lib.linf_norm_dist_forward(*a, y.data_ptr(), p, stream), "lp forward"), flush, n=5, warm=2)
         b = (g.data_ptr(), x.data_ptr(), w.data_ptr(), y.data_ptr(), Bq, CO, CI, 1, 1)
         t_gx = _timed_us(torch, lambda: _lib.check(lib.linf_norm_dist_backward_input(*b, gx.data_ptr(), p, stream), "lp gx"), flush, n=5, warm=2)
         t_gw = _timed_us(torch, lambda: _lib.check(lib.linf_norm_dist_backward_weight(*b, gw.data_ptr(), p, stream), "lp gw"), flush, n=5, warm=2)
-        import math
-        sq = int(math.log2(p))
-        ops_f, ops_b = 3 + sq, 4 + sq          # see ops_per_term; the forward also runs the max pass (2 ops per term)
-        lp[f"p{int(p)}"] = {
-            "us_forward": t_f, "us_grad_input": t_gx, "us_grad_weight": t_gw,
-            "fwd_terms_per_s": terms / (t_f * 1e-6), "fwd_bwd_terms_per_s": terms / ((t_f + t_gx + t_gw) * 1e-6),
-            "frac_fp32_issue_forward": (ops_f + 2) * terms / (t_f * 1e-6) / lane_peak,
-            "frac_fp32_issue_backward": 2 * ops_b * terms / ((t_gx + t_gw) * 1e-6) / lane_peak}
+        entry = {"us_forward": t_f, "us_grad_input": t_gx, "us_grad_weight": t_gw,
+                 "fwd_terms_per_s": terms / (t_f * 1e-6), "fwd_bwd_terms_per_s": terms / ((t_f + t_gx + t_gw) * 1e-6)}
+        if p == int(p):
+            sq = int(math.log2(p))
+            ops_f, ops_b = 3 + sq, 4 + sq          # see ops_per_term; the forward also runs the max pass (2 ops per term)
+            entry["frac_fp32_issue_forward"] = (ops_f + 2) * terms / (t_f * 1e-6) / lane_peak
+            entry["frac_fp32_issue_backward"] = 2 * ops_b * terms / ((t_gx + t_gw) * 1e-6) / lane_peak
+            lp[f"p{int(p)}"] = entry
+        else:
+            # a p met while annealing: one log2 / exp2 pair per term and pass on the special-function unit
+            # (16 lanes per SM and clock), so 2 MUFU operations per term bound each pass
+            mufu_peak = lane_peak / 8.0
+            entry["bound"] = "mufu"
+            entry["frac_mufu_forward"] = 2.0 * terms / (t_f * 1e-6) / mufu_peak
+            entry["frac_mufu_backward"] = 2.0 * 2.0 * terms / ((t_gx + t_gw) * 1e-6) / mufu_peak
+            lp[f"p{p:g}"] = entry
     out["lp"] = lp
     del x, w, g, y, gx, gw
 
