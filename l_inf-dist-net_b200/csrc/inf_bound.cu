@@ -93,7 +93,8 @@ constexpr int SMEM_BYTES = STAGES * STAGE_FLOATS * 4;
 struct BoundParams {
     const float* xl; const float* xu; const float* w; float* yl; float* yu;
     int M, N, K, G, lda, ldo, tiles_m, tiles_n, KT;
-    Post post;             // per-channel epilogue of the stored bounds (all null: none)
+    int ksplit;            // CTAs per output tile, each with an equal share of the k-tiles (1 or 2)
+    Post post;             // per-channel epilogue of the stored bounds (all null: none; ksplit == 1 only)
 };
 
 __device__ __forceinline__ void load_stage(float* stage, const BoundParams& p, int g, int m0, int n0,
@@ -170,7 +171,7 @@ __device__ __forceinline__ void tile_step(const float* __restrict__ Ls, const fl
 // element of the tile's rows that breaks "lower <= upper, both finite".
 template <bool FAST>
 __device__ __forceinline__ bool run_tile(float* smem, const BoundParams& p, int g, int m0, int n0,
-                                         int tid, int row_off, int col_off,
+                                         int kt_begin, int kt_end, int tid, int row_off, int col_off,
                                          float (&accL)[NO], float (&accU)[NO]) {
     bool bad = false;
 #pragma unroll
@@ -178,14 +179,14 @@ __device__ __forceinline__ bool run_tile(float* smem, const BoundParams& p, int 
     __syncthreads();
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < p.KT) load_stage(smem + s * STAGE_FLOATS, p, g, m0, n0, s, tid);
+        if (kt_begin + s < kt_end) load_stage(smem + s * STAGE_FLOATS, p, g, m0, n0, kt_begin + s, tid);
         cp_async_commit();
     }
     int rd = 0, wr = STAGES - 1;
-    for (int kt = 0; kt < p.KT; ++kt) {
+    for (int kt = kt_begin; kt < kt_end; ++kt) {
         cp_async_wait<STAGES - 2>();
         __syncthreads();
-        if (kt + STAGES - 1 < p.KT) load_stage(smem + wr * STAGE_FLOATS, p, g, m0, n0, kt + STAGES - 1, tid);
+        if (kt + STAGES - 1 < kt_end) load_stage(smem + wr * STAGE_FLOATS, p, g, m0, n0, kt + STAGES - 1, tid);
         cp_async_commit();
         const float* st = smem + rd * STAGE_FLOATS;
         if (FAST) {
@@ -218,18 +219,38 @@ inf_bound_tiled_kernel(const BoundParams p) {
     const int row_off = wm * 32 + lm, col_off = wn * (8 * TN) + ln;
 
     const int tiles_per_group = p.tiles_m * p.tiles_n;
-    const int tile = blockIdx.x;
+    // With ksplit = 2 two CTAs share an output tile, each over one half of the k-tiles.  Both bounds are maxima of
+    // non-negative numbers that start from 0, so the halves are combined with an integer atomicMax on the zero-filled
+    // outputs (non-negative floats order like their bit patterns): exact, whichever CTA comes first.
+    const int tile = (int)blockIdx.x / p.ksplit, part = (int)blockIdx.x - tile * p.ksplit;
+    const int kt_begin = p.KT * part / p.ksplit, kt_end = p.KT * (part + 1) / p.ksplit;
     const int g = tile / tiles_per_group, tg = tile - g * tiles_per_group;
     const int n0 = (tg / p.tiles_m) * BN, m0 = (tg % p.tiles_m) * BM;
 
     float accL[NO], accU[NO];
-    const bool bad = run_tile<true>(smem, p, g, m0, n0, tid, row_off, col_off, accL, accU);
+    const bool bad = run_tile<true>(smem, p, g, m0, n0, kt_begin, kt_end, tid, row_off, col_off, accL, accU);
     const bool any_bad = __syncthreads_or(bad);
     if (!any_bad) {
 #pragma unroll
         for (int e = 0; e < NO; ++e) accL[e] = 0.f - accL[e];
     } else {
-        run_tile<false>(smem, p, g, m0, n0, tid, row_off, col_off, accL, accU);
+        run_tile<false>(smem, p, g, m0, n0, kt_begin, kt_end, tid, row_off, col_off, accL, accU);
+    }
+    if (p.ksplit > 1) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int m = m0 + row_off + 4 * i;
+#pragma unroll
+            for (int j = 0; j < TN; ++j) {
+                const int n = n0 + col_off + 8 * j;
+                if (m < p.M && n < p.N) {
+                    const size_t o = (size_t)m * p.ldo + (size_t)g * p.N + n;
+                    atomicMax(reinterpret_cast<int*>(p.yl + o), __float_as_int(accL[i * TN + j]));
+                    atomicMax(reinterpret_cast<int*>(p.yu + o), __float_as_int(accU[i * TN + j]));
+                }
+            }
+        }
+        return;
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -247,6 +268,17 @@ inf_bound_tiled_kernel(const BoundParams p) {
                 }
             }
         }
+    }
+}
+
+// The per-channel epilogue as a pass of its own, for launches that combined partial results in memory.
+__global__ void __launch_bounds__(256)
+inf_bound_post_kernel(float* __restrict__ yl, float* __restrict__ yu, size_t n, int CO, Post post) {
+    for (size_t e = (size_t)blockIdx.x * 256 + threadIdx.x; e < n; e += (size_t)gridDim.x * 256) {
+        const int c = (int)(e % (size_t)CO);
+        const float lo = post_apply(post, yl[e], c), up = post_apply(post, yu[e], c);
+        yl[e] = post.negate ? up : lo;
+        yu[e] = post.negate ? lo : up;
     }
 }
 
@@ -268,14 +300,33 @@ int inf_bound(const float* xl, const float* xu, const float* w, const Dims& d,
     p.xl = xl; p.xu = xu; p.w = w; p.yl = yl; p.yu = yu;
     p.M = d.R; p.N = d.COg; p.K = d.CIg; p.G = d.G; p.lda = d.CI; p.ldo = d.CO;
     p.post = post;
+    p.ksplit = 1;
     p.tiles_m = (d.R + BM - 1) / BM; p.tiles_n = (d.COg + BN - 1) / BN;
     p.KT = (d.CIg + BK - 1) / BK;
+    int grid = p.tiles_m * p.tiles_n * d.G;
+    {
+        // Output tiles that leave much of their last wave of CTAs idle, with long rows: two CTAs per tile (1.58 ->
+        // 1.2 ms at B = 512, Din = 3072, Dout = 5120: 640 tiles on 444 CTA slots).
+        const int slots = 3 * sm_count();
+        auto fill = [&](int n) { return (double)n / ((double)((n + slots - 1) / slots) * slots); };
+        if (p.KT >= 64 && fill(2 * grid) > 1.15 * fill(grid)) {
+            const size_t bytes = (size_t)d.R * d.CO * sizeof(float);
+            if (cudaMemsetAsync(yl, 0, bytes, st) != cudaSuccess || cudaMemsetAsync(yu, 0, bytes, st) != cudaSuccess)
+                return LINF_ERR_LAUNCH;
+            p.ksplit = 2;
+            grid *= 2;
+        }
+    }
     // opting in to > 48 KB of dynamic shared memory is per function and per device; repeating it on
     // every call is cheap and keeps the launcher free of per-device state
     if (cudaFuncSetAttribute(inf_bound_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              SMEM_BYTES) != cudaSuccess)
         return LINF_ERR_LAUNCH;
-    inf_bound_tiled_kernel<<<p.tiles_m * p.tiles_n * d.G, NT, SMEM_BYTES, st>>>(p);
+    inf_bound_tiled_kernel<<<grid, NT, SMEM_BYTES, st>>>(p);
+    if (p.ksplit > 1 && (post.sub != nullptr || post.add != nullptr || post.negate)) {
+        const size_t n = (size_t)d.R * d.CO;
+        inf_bound_post_kernel<<<2 * sm_count(), 256, 0, st>>>(yl, yu, n, d.CO, post);
+    }
     return launch_status();
 }
 

@@ -132,11 +132,12 @@ def test_inf_bound_bit_exact(cuda, lib, shape):
     assert (yl_ref <= yu_ref).all()
 
 
+@pytest.mark.parametrize("CI", [64, 2048], ids=["short_rows", "rows_split_over_two_ctas"])
 @pytest.mark.parametrize("kind", ["swapped", "nan", "inf", "degenerate"])
-def test_inf_bound_irregular_inputs(cuda, lib, kind):
+def test_inf_bound_irregular_inputs(cuda, lib, kind, CI):
     """lower > upper, NaN and infinities leave the fast rule's domain: the result must still be
-    the literal rule's, bit for bit."""
-    B, CI, CO = 130, 64, 200
+    the literal rule's, bit for bit (also when two CTAs share a tile's reduction and merge in memory)."""
+    B, CO = 130, 200
     x, w, _ = make_inputs(B, CI, CO, 1, 1, seed=77)
     lo = (x - 0.05).astype(np.float32); up = (x + 0.05).astype(np.float32)
     if kind == "swapped":
