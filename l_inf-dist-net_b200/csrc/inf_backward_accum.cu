@@ -23,9 +23,9 @@ namespace linf {
 namespace {
 
 constexpr unsigned FULL = 0xffffffffu;
-constexpr int SB = 512;          // sources per staged block
-constexpr int SBP = SB + 4;      // pitch of a row's staged block: neighbouring rows land 4 banks apart, so the
-                                 // staging stores of a warp (8 rows x 4 sources) touch 32 different banks
+constexpr int SB_MAX = 512;      // sources per staged block (template parameter SB: 512 or 256); a row's staged block
+                                 // has a pitch of SB + 4 words: neighbouring rows land 4 banks apart, so the staging
+                                 // stores of a warp (8 rows x 4 sources) touch 32 different banks
 
 // One batch of up to 32 sources, one per lane: bin `idx` (idx >= nb = no source / dropped) and
 // signed value `v`.
@@ -88,10 +88,11 @@ __device__ __forceinline__ void add_batch(float* __restrict__ acc, const Batch& 
 // row's bins, its running popcount, and dense accumulators addressed through them -- and expands
 // to the full row (zeros elsewhere) when it writes it out.  Shared memory per row drops from
 // 4 * CIg bytes to CIg / 4 + 4 * sources, which keeps 24 warps per SM at CIg = 5120.
-template <bool COMPACT>
-__global__ void __launch_bounds__(256)
+template <bool COMPACT, int SB>
+__global__ void __launch_bounds__(SB == 512 ? 256 : 640)
 inf_backward_weight_accum_kernel(const float* __restrict__ gout, const int* __restrict__ pos, Dims d,
                                  float* __restrict__ dst, int nbp, int vec_out) {
+    constexpr int SBP = SB + 4;
     extern __shared__ __align__(16) float smem_f[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int rpc = blockDim.x >> 5;
@@ -217,9 +218,30 @@ int inf_backward_weight_accum(const float* g, const int* pos, const Dims& d, flo
     // long rows with few sources, and enough rows for occupancy to matter: accumulators only for
     // the bins that occur (measured at R = 512, CO = 5120: 61 us vs 76 us at CIg = 5120, but
     // 59 us vs 50 us at CIg = 3072 and 23 us vs 16 us for the 10 rows of a classifier layer)
-    const bool compact = d.CIg >= 4096 && d.R <= SB && d.CO >= 1024;
+    const bool compact = d.CIg >= 4096 && d.R <= SB_MAX && d.CO >= 1024;
     const int nbw4 = (((d.CIg + 31) >> 5) + 3) & ~3;
-    const size_t per_row = (compact ? (size_t)(2 * nbw4 + SB) * 4 : (size_t)nbp * 4) + (size_t)SBP * 8;
+    if (!compact) {
+        // Short rows: when the rows one SM has to produce (CO / SMs) fit its shared memory at once, they are
+        // dealt to two CTAs per SM with one warp per row and half-size staging blocks, so that the whole
+        // launch is ONE wave of CTAs with all of an SM's rows in flight together (at B = 512, Din = 784,
+        // Dout = 5120: 285 CTAs of 18 warps on 296 slots, instead of 640 CTAs of 8 warps on 444 slots).
+        constexpr int SBS = 256;
+        const int sms = sm_count();
+        const int rows_per_sm = (d.CO + sms - 1) / sms;
+        const int rpc_w = (rows_per_sm + 1) / 2;
+        const size_t per_row_w = (size_t)nbp * 4 + (size_t)(SBS + 4) * 8;
+        if (rpc_w >= 4 && rpc_w <= 20 && 2 * rpc_w * per_row_w <= 220 * 1024 && d.CO >= 4 * sms) {
+            const size_t smem_w = (size_t)rpc_w * per_row_w;
+            auto kern_w = inf_backward_weight_accum_kernel<false, SBS>;
+            if (cudaFuncSetAttribute(kern_w, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)limit) != cudaSuccess)
+                return LINF_ERR_LAUNCH;
+            const int vec = ((d.CIg & 3) == 0 && (reinterpret_cast<uintptr_t>(gw) & 15u) == 0) ? 1 : 0;
+            kern_w<<<(d.CO + rpc_w - 1) / rpc_w, 32 * rpc_w, smem_w, st>>>(g, pos, d, gw, nbp, vec);
+            return launch_status();
+        }
+    }
+    constexpr int SBP = SB_MAX + 4;
+    const size_t per_row = (compact ? (size_t)(2 * nbw4 + SB_MAX) * 4 : (size_t)nbp * 4) + (size_t)SBP * 8;
     if (per_row > limit) return -1;
     // Rows per CTA.  Neighbouring rows share the sectors of the strided sources: 8 rows use every
     // sector whole, but two CTAs per SM (one staging while the other adds) are worth more.
@@ -227,7 +249,7 @@ int inf_backward_weight_accum(const float* g, const int* pos, const Dims& d, flo
     while (rpc > 1 && (size_t)rpc * per_row > limit) rpc >>= 1;
     while (rpc > 2 && (size_t)rpc * per_row > 100 * 1024) rpc >>= 1;
     const size_t smem = (size_t)rpc * per_row;
-    auto kern = compact ? inf_backward_weight_accum_kernel<true> : inf_backward_weight_accum_kernel<false>;
+    auto kern = compact ? inf_backward_weight_accum_kernel<true, SB_MAX> : inf_backward_weight_accum_kernel<false, SB_MAX>;
     if (smem > 40 * 1024 &&
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)limit) != cudaSuccess)
         return LINF_ERR_LAUNCH;
