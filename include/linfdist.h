@@ -268,12 +268,14 @@ int linf_adamw_step(float* param, const float* grad, float* exp_avg, float* exp_
 
 /*
  * Process-wide switches between kernel variants that give identical results.  NOT thread safe, and
- * key 0 changes what linf_inf_dist_forward_workspace_bytes answers: set it while no call is in flight.
+ * keys 0, 4 and 5 change what linf_inf_dist_forward_workspace_bytes answers: set it while no call is in flight.
  *   key 0  tiled inf-dist forward variant (0 = default; the table is in csrc/inf_forward.cu)
  *   key 1  1 = run a partial last wave of output tiles as half-width tiles (default), 0 = never
  *   key 2  (value ignored) returns 1 if a bounded wait of the TMA-loader variant ever ran out, else 0
  *   key 3  1 = skip the direct-accumulation grad_input kernel, 0 = use it where it applies (default)
  *   key 4  k-splitting of the forward: 0 = by shape (default), 1 = whenever scratch is given, 2 = never
+ *   key 5  width of the forward's output tiles: 0 = by shape (default), 1 = 64 columns, 2 = 48 columns wherever
+ *          that kernel applies
  * Returns LINF_OK, the answer of key 2, or LINF_ERR_DIMS for an unknown key / value.
  */
 int linf_tune_set(int key, int value);

@@ -83,6 +83,7 @@ int SideLease::join(cudaStream_t into) {
 extern int inf_forward_variant;
 extern int inf_forward_tail;
 extern int inf_forward_split;
+extern int inf_forward_width;
 int inf_forward_tma_gave_up();
 
 }  // namespace linf
@@ -120,6 +121,7 @@ int linf_tune_set(int key, int value) {
     if (key == 1 && (value == 0 || value == 1)) { inf_forward_tail = value; return LINF_OK; }
     if (key == 3 && (value == 0 || value == 1)) { inf_backward_path = value; return LINF_OK; }
     if (key == 4 && value >= 0 && value <= 2) { inf_forward_split = value; return LINF_OK; }
+    if (key == 5 && value >= 0 && value <= 2) { inf_forward_width = value; return LINF_OK; }
     if (key == 2) return inf_forward_tma_gave_up();   // 1 = a bounded wait of the TMA loader ran out since the library was loaded
     return LINF_ERR_DIMS;
 }

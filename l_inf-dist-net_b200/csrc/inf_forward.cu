@@ -613,7 +613,9 @@ struct Variant {
     Kernels main;      // 64 x 64 output tiles (8 x 4 outputs per thread), 3 CTAs per SM
     Kernels tail;      // 64 x 32 output tiles (8 x 2 outputs per thread) for a partial last wave
     int tma;           // 0: cp.async loader; 1: TMA, padded boxes; 2: TMA, 128-byte swizzle
+    Kernels narrow;    // 64 x 48 output tiles (8 x 3 outputs per thread), 3 CTAs per SM, loader of `main`; nt == 0: none
 };
+constexpr Kernels kNoKernels{0, 0, 0, 0, 0, 0, nullptr, nullptr};
 
 template <class GEO, int LOADER = 0>
 constexpr Kernels make_kernels() {
@@ -622,23 +624,26 @@ constexpr Kernels make_kernels() {
 }
 
 // All variants: CTAs of 128 threads, 8 x 4 outputs per thread, 3 CTAs per SM.  Measured on one B200, us per
-// forward with arg-max at B = 512, Dout = 5120 and Din = 784 / 1024 / 3072 / 5120 (whole tiles + tail launch
-// below 1536, k-split above), same box:
+// forward with arg-max at B = 512, Dout = 5120 and Din = 784 / 1024 / 3072 / 5120 (whole 64 x 64 tiles + tail
+// launch below 1536, k-split above), same box:
 //   0: 196 / 238 / 592 / 942      1: 202 / 242 / 606 / 965      (0 with 4 stages: 200 / 239 / 600 / 950)
 // and on another box   1: 192 / 230 / 596 / 954      2: 190 / 237 / 620 / 997      3: 204 / 247 / 611 / 962
 // (variants 1-3 with the register budget of 4 CTAs per SM: 206-218 / 249-263 / 653-678 / 1022-1085).
+// Variant 0 with 64 x 48 tiles (`narrow`, 149 registers, whole tiles, no tail): 178 / 217 / 584 / 951; the same
+// with the register budget of 4 CTAs per SM (spills 108 bytes): 189 / 232 / 617 / 1004.
 const Variant kVariants[] = {
     // 0: 32-term k-tiles fetched by TMA with the 128-byte swizzle (unpadded rows, 3 stages), 8-term windows (default)
-    {make_kernels<Geo<128, 4, 32, 3, 8, 0>, 2>(), make_kernels<Geo<128, 2, 32, 4, 8>>(), 2},
+    {make_kernels<Geo<128, 4, 32, 3, 8, 0>, 2>(), make_kernels<Geo<128, 2, 32, 4, 8>>(), 2,
+     make_kernels<Geo<128, 3, 32, 3, 8, 0>, 2>()},
     // 1: 32-term k-tiles (cp.async, 3 stages), 8-term tracking windows
-    {make_kernels<Geo<128, 4, 32, 3, 8>>(), make_kernels<Geo<128, 2, 32, 4, 8>>(), 0},
+    {make_kernels<Geo<128, 4, 32, 3, 8>>(), make_kernels<Geo<128, 2, 32, 4, 8>>(), 0, kNoKernels},
     // 2: 16-term k-tiles (cp.async, 4 stages), 8-term tracking windows
-    {make_kernels<Geo<128, 4, 16, 3, 8>>(), make_kernels<Geo<128, 2, 16, 4, 8>>(), 0},
+    {make_kernels<Geo<128, 4, 16, 3, 8>>(), make_kernels<Geo<128, 2, 16, 4, 8>>(), 0, kNoKernels},
     // 3: 16-term k-tiles, one tracking window per k-tile
-    {make_kernels<Geo<128, 4, 16, 3, 16>>(), make_kernels<Geo<128, 2, 16, 4, 16>>(), 0},
+    {make_kernels<Geo<128, 4, 16, 3, 16>>(), make_kernels<Geo<128, 2, 16, 4, 16>>(), 0, kNoKernels},
     // 4: as 3 with TMA and padded boxes (measured 7-14 % slower than 3: the extra four columns per row cost L2
     //    traffic)
-    {make_kernels<Geo<128, 4, 16, 3, 16>, 1>(), make_kernels<Geo<128, 2, 16, 4, 16>>(), 1},
+    {make_kernels<Geo<128, 4, 16, 3, 16>, 1>(), make_kernels<Geo<128, 2, 16, 4, 16>>(), 1, kNoKernels},
 };
 constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
 
@@ -654,7 +659,8 @@ int inf_forward_tma_gave_up() {
 
 int inf_forward_variant = 0;   // index into kVariants (benchmarking knob)
 int inf_forward_tail = 1;      // 1: a partial last wave runs as half-width tiles; 0: never
-int inf_forward_split = 0;     // 0: k-splitting by the rule of want_split; 1: whenever scratch is given; 2: never
+int inf_forward_split = 0;     // 0: k-splitting by the rule of make_plan; 1: whenever scratch is given; 2: never
+int inf_forward_width = 0;     // 0: tile width by the rule of make_plan; 1: 64 columns always; 2: 48 wherever they exist
 
 // Shapes the tiled path accepts (window numbers travel as 16 bits: at most 65535 windows per row).
 static bool tiled_ok(const float* x, const float* w, const Dims& d) {
@@ -668,31 +674,78 @@ static const Variant& cur_variant() {
     return kVariants[(v >= 0 && v < kNumVariants) ? v : 0];
 }
 
-static int tiled_tiles(const Dims& d, const Variant& v) {
-    return ((d.R + v.main.bm - 1) / v.main.bm) * ((d.COg + v.main.bn - 1) / v.main.bn) * d.G;
+static int tiled_tiles(const Dims& d, const Kernels& k) {
+    return ((d.R + k.bm - 1) / k.bm) * ((d.COg + k.bn - 1) / k.bn) * d.G;
 }
 
-// Splitting k-tiles across CTAs pays when whole tiles would leave a large part of the last
-// wave of CTAs idle -- unless the rows are short: every CTA of a split launch ends with a merge
-// and an arg-max rescan at the same moment, which costs more than the idle part of a wave when
-// the k loop itself is short (measured: 217 us split vs 209 us unsplit at K = 784, 956 us vs
-// 1063 us at K = 5120).  With fewer tiles than CTA slots there is nothing to lose: split.
-static bool want_split(const Dims& d, const Variant& v) {
-    if (inf_forward_split == 1) return true;
-    if (inf_forward_split == 2) return false;
+// The TMA loader zero-fills past the END OF A ROW OF THE MATRIX.  With groups the k-tiles of one
+// group are followed by the next group's columns, so a ragged last k-tile is only right for G = 1.
+static bool tma_shape_ok(const Dims& d, int bk) { return (d.G == 1 || d.CIg % bk == 0) && d.CIg >= 32 && d.R >= 1; }
+
+// How a shape is run: which tile geometry, whole tiles or k-tiles dealt evenly to the CTAs (scratch).
+// A warp issues its subtract / max pairs every 5.5 cycles when it is alone on its scheduler and the
+// scheduler one pair every 2.9 cycles when it has three or four warps, so what a wave of CTAs costs
+// depends on how many CTAs share an SM and on the outputs per thread, not on how full the wave is.
+// kWave: time of a wave with c CTAs per SM, in units of a full wave of 64 x 64 tiles (which takes
+// about 12 + 0.115 * Din microseconds), fitted to measurements on one B200 over 21 shapes
+// (B = 64 ... 2048, Din = 784 ... 12288, Dout = 512 ... 10240; the pick is within 4 % of the best of
+// the three on all but one of them, 8 % there).  The k-split costs its share of a full wave plus
+// 20 + 0.006 * Din microseconds for the parked partial results, the merge and an arg-max rescan that
+// all CTAs reach at the same moment; it has to win by 3 %.
+struct Plan { bool narrow, split; };
+
+constexpr double kWaveMain[5] = {0, 0.387, 0.624, 1.0, 1.0};       // 8 x 4 outputs per thread, at most 3 CTAs per SM
+constexpr double kWaveNarrow[5] = {0, 0.29, 0.468, 0.765, 0.765};  // 8 x 3
+constexpr double kWaveTail[5] = {0, 0.22, 0.33, 0.60, 0.72};       // 8 x 2, at most 4 CTAs per SM, cp.async loader
+
+static double waves_cost(int ctas, int per_sm, const double (&wave)[5]) {
+    const int sms = sm_count(), slots = per_sm * sms;
+    const int rest = ctas % slots;
+    return (ctas / slots) * wave[per_sm] + (rest ? wave[(rest + sms - 1) / sms] : 0.0);
+}
+
+// CTAs of the tail launch that the launcher would use for this shape with 64 x 64 tiles (0: none),
+// and the tiles left to the main launch.
+static int tail_split(const Dims& d, const Variant& v, int* main_tiles) {
+    const int tiles_m = (d.R + v.main.bm - 1) / v.main.bm;
+    const int tiles = tiled_tiles(d, v.main), slots = v.main.min_blocks * sm_count();
+    *main_tiles = tiles;
+    if (inf_forward_tail == 0 || d.G != 1 || v.tail.bk != v.main.bk) return 0;
+    const int cols_main = ((tiles / slots) * slots) / tiles_m;
+    const int full = cols_main * tiles_m, rest = tiles - full;
+    const int tail_ctas = ((d.COg + v.tail.bn - 1) / v.tail.bn - (v.main.bn / v.tail.bn) * cols_main) * tiles_m;
+    if (!(rest > 0 && rest * 10 <= slots * 8 && tail_ctas > 0 && tail_ctas <= v.tail.min_blocks * sm_count())) return 0;
+    *main_tiles = full;
+    return tail_ctas;
+}
+
+static Plan make_plan(const Dims& d, const Variant& v, bool scratch) {
     const int slots = v.main.min_blocks * sm_count();
-    const int tiles = tiled_tiles(d, v);
-    const int waves = (tiles + slots - 1) / slots;
-    if ((double)tiles / ((double)waves * slots) >= 0.9) return false;
-    return tiles < slots || d.CIg >= 1536;
+    const int tiles = tiled_tiles(d, v.main);
+    const bool can_narrow = v.narrow.nt != 0 && inf_forward_width != 1 && d.COg >= v.narrow.bn &&
+                            (v.tma == 0 || tma_shape_ok(d, v.narrow.bk));
+    const bool can_split = scratch && inf_forward_split != 2;
+    const double wave_us = 12.0 + 0.115 * d.CIg;
+    int main_tiles;
+    const int tail_ctas = tail_split(d, v, &main_tiles);
+    double c_main = wave_us * (waves_cost(main_tiles, v.main.min_blocks, kWaveMain) +
+                               (tail_ctas ? waves_cost(tail_ctas, v.tail.min_blocks, kWaveTail) : 0.0));
+    double c_narrow = can_narrow ? wave_us * waves_cost(tiled_tiles(d, v.narrow), v.narrow.min_blocks, kWaveNarrow) : 1e30;
+    double c_split = can_split ? 1.03 * (wave_us * tiles / slots + 20.0 + 0.006 * d.CIg) : 1e30;
+    if (can_narrow && inf_forward_width == 2) c_narrow = 0.0;
+    if (can_split && inf_forward_split == 1) c_split = -1.0;
+    Plan pl;
+    pl.split = c_split < c_main && c_split < c_narrow;
+    pl.narrow = !pl.split && c_narrow < c_main;
+    return pl;
 }
 
 size_t inf_forward_workspace(const Dims& d) {
     if (d.HW != 1 || (d.CIg % 4) != 0 || d.COg < 32) return 0;
     const Variant& v = cur_variant();
-    if (!want_split(d, v)) return 0;
+    if (!make_plan(d, v, true).split) return 0;
     const size_t n_cta = (size_t)v.main.min_blocks * sm_count();
-    return align256((size_t)tiled_tiles(d, v) * sizeof(int)) +
+    return align256((size_t)tiled_tiles(d, v.main) * sizeof(int)) +
            n_cta * 2 * v.main.bm * v.main.bn * (sizeof(float) + sizeof(int));
 }
 
@@ -732,10 +785,6 @@ static bool tma_matrix(const float* base, size_t rows, size_t cols, size_t pitch
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// The TMA loader zero-fills past the END OF A ROW OF THE MATRIX.  With groups the k-tiles of one
-// group are followed by the next group's columns, so a ragged last k-tile is only right for G = 1.
-static bool tma_shape_ok(const Dims& d, int bk) { return (d.G == 1 || d.CIg % bk == 0) && d.CIg >= 32 && d.R >= 1; }
-
 static int launch_tiled(const Kernels& k, const TiledParams& p, bool track, cudaStream_t st) {
     auto kern = track ? k.track : k.plain;
     // opting in to > 48 KB of dynamic shared memory is per function and per device; it is cheap
@@ -757,11 +806,25 @@ int inf_forward(const float* x, const float* w, const Dims& d, float* y, int* po
         return launch_status();
     }
     const Variant& v = cur_variant();
-    const Kernels* use = &v.main;
+    const size_t need = inf_forward_workspace(d);
+    const bool scratch = ws != nullptr && need != 0;
+    if (scratch && (ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 255u))) return LINF_ERR_WORKSPACE;
+    Plan plan = make_plan(d, v, scratch);
     TiledParams p;
     p.x = x; p.w = w; p.y = y; p.pos = pos;
     p.M = d.R; p.N = d.COg; p.K = d.CIg; p.G = d.G;
     p.lda = d.CI; p.ldo = d.CO;
+    const Kernels* use = plan.narrow ? &v.narrow : &v.main;
+    if (v.tma) {
+        const int pad = v.tma == 1 ? 4 : 0;
+        const bool ok = tma_shape_ok(d, use->bk) &&
+                        tma_matrix(x, (size_t)d.R, (size_t)d.CI, (size_t)d.CI, use->bk + pad, use->bm, &p.tm_x, v.tma == 2) &&
+                        tma_matrix(w, (size_t)d.CO, (size_t)d.CIg, (size_t)d.CIg, use->bk + pad, use->bn, &p.tm_w, v.tma == 2);
+        if (!ok) {      // 64 x 64 tiles with the cp.async loader
+            use = &kVariants[v.tma == 1 ? 3 : 1].main;
+            plan.narrow = false;
+        }
+    }
     p.tiles_m = (d.R + use->bm - 1) / use->bm; p.tiles_n = (d.COg + use->bn - 1) / use->bn;
     p.KT = (d.CIg + use->bk - 1) / use->bk;
     const int tiles = p.tiles_m * p.tiles_n * d.G;
@@ -771,9 +834,7 @@ int inf_forward(const float* x, const float* w, const Dims& d, float* y, int* po
     p.tile0 = 0;
     p.post = post;
     const int slots = use->min_blocks * sm_count();
-    const size_t need = inf_forward_workspace(d);
-    if (ws != nullptr && need != 0) {
-        if (ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 255u)) return LINF_ERR_WORKSPACE;
+    if (plan.split) {
         const size_t tick_bytes = align256((size_t)tiles * sizeof(int));
         const long long total = (long long)tiles * p.KT;
         p.slots_cta = slots;
@@ -783,24 +844,13 @@ int inf_forward(const float* x, const float* w, const Dims& d, float* y, int* po
         p.part_cid = reinterpret_cast<int*>(p.part_val + (size_t)p.slots_cta * 2 * use->bm * use->bn);
         if (cudaMemsetAsync(p.tickets, 0, tick_bytes, st) != cudaSuccess) return LINF_ERR_LAUNCH;
     }
-    if (v.tma) {
-        const int pad = v.tma == 1 ? 4 : 0;
-        const bool ok = tma_shape_ok(d, use->bk) &&
-                        tma_matrix(x, (size_t)d.R, (size_t)d.CI, (size_t)d.CI, use->bk + pad, use->bm, &p.tm_x, v.tma == 2) &&
-                        tma_matrix(w, (size_t)d.CO, (size_t)d.CIg, (size_t)d.CIg, use->bk + pad, use->bn, &p.tm_w, v.tma == 2);
-        if (!ok) use = &kVariants[v.tma == 1 ? 3 : 1].main;      // same geometry with the cp.async loader
-    }
     // Whole tiles that end in a partial wave of CTAs (or never fill one): the columns of that
     // partial wave are run as tiles of half the width by the tail kernels, twice as many CTAs.
     // Only whole columns of tiles change hands, so the two launches cover disjoint column ranges.
-    if (p.tickets == nullptr && inf_forward_tail != 0 && d.G == 1 && v.tail.bk == use->bk) {
-        const int cols_main = ((tiles / slots) * slots) / p.tiles_m;     // tile columns of the whole waves
-        const int full = cols_main * p.tiles_m, rest = tiles - full;
-        const int tail_slots = v.tail.min_blocks * sm_count();
-        const int tail_tiles_n = (d.COg + v.tail.bn - 1) / v.tail.bn;
-        const int ratio = use->bn / v.tail.bn;
-        const int tail_ctas = (tail_tiles_n - ratio * cols_main) * p.tiles_m;
-        if (rest > 0 && rest * 10 <= slots * 8 && tail_ctas > 0 && tail_ctas <= tail_slots) {
+    if (p.tickets == nullptr && !plan.narrow) {
+        int full;
+        const int tail_ctas = tail_split(d, v, &full);
+        if (tail_ctas > 0 && v.tail.bk == use->bk) {
             int rc = LINF_OK;
             if (full > 0) {
                 p.n_cta = full;
@@ -808,8 +858,8 @@ int inf_forward(const float* x, const float* w, const Dims& d, float* y, int* po
                 if (rc) return rc;
             }
             TiledParams q = p;
-            q.tiles_n = tail_tiles_n;
-            q.tile0 = ratio * cols_main * p.tiles_m;
+            q.tiles_n = (d.COg + v.tail.bn - 1) / v.tail.bn;
+            q.tile0 = (use->bn / v.tail.bn) * full;     // whole tile columns changed hands: tile index scales with the width
             q.n_cta = tail_ctas;
             return launch_tiled(v.tail, q, pos != nullptr, st);
         }

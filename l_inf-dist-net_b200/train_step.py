@@ -12,7 +12,7 @@ from . import _lib
 from .adamw import AdamW
 from .bound_module import BoundFinalIdentity, Predictor
 from .nets import MLP, MLPFeature, Model
-from .norm_dist import set_p_norm
+from .norm_dist import NormDistConv, get_p_norm, set_p_norm, _row_gates
 
 
 def hinge(mix=0.75):
@@ -75,6 +75,8 @@ class DataParallelStep:
     averaged gradient before its next use); only the order of launches differs.  With one rank
     there is no communication and the same schedule overlaps the optimiser with the passes."""
 
+    FIRST_CHUNKS = 4      # row ranges the first layer's weight is exchanged, updated and run in
+
     def __init__(self, net, optimizer, eager_bytes=None, urgent_group=True):
         import torch.distributed as dist
         self.net, self.opt = net, optimizer
@@ -111,6 +113,16 @@ class DataParallelStep:
                 for b in self.buffers:
                     b.data = self.flat_buffers[off:off + b.numel()].view_as(b)
                     off += b.numel()
+        # ... and in row ranges: the all-reduce of range c, the optimiser on range c, and the part of the
+        # next forward that needs range c (a column range of the layer's output) form a pipeline, so that
+        # only the first range's exchange is exposed (norm_dist._row_gates; dense p = inf layers only).
+        self.first_chunks = None
+        if self.urgent is not None and self.first.dim() >= 2 and self.first.size(0) % (64 * self.FIRST_CHUNKS) == 0:
+            owner = next((m for m in net.modules() if isinstance(m, NormDistConv) and m.weight is self.first), None)
+            if owner is not None and owner.kernel_size == 1 and owner.group == 1 and self.first.is_contiguous():
+                n = self.first.size(0) // self.FIRST_CHUNKS
+                self.first_chunks = [(c * n, (c + 1) * n, torch.cuda.Event()) for c in range(self.FIRST_CHUNKS)]
+        self.gated = None               # id of the parameter whose forward waits through norm_dist._row_gates
         self.events = {}
         self.trace = None               # set to a list to record, per waiting layer, how long the forward stalled
         self.sent, self.held = 0, []
@@ -130,8 +142,10 @@ class DataParallelStep:
                 marks[0].record(cur)
             for q in own:
                 ev = self.events.get(id(q))
-                if ev is not None:
+                if ev is not None and id(q) != self.gated:
                     cur.wait_event(ev)
+                elif ev is not None:
+                    cur.wait_event(self.first_chunks[0][2])     # the later ranges are waited for inside the operator
             if marks is not None:
                 marks[1].record(cur)
                 self.trace.append((type(module).__name__ + str(tuple(own[0].shape)), marks))
@@ -145,6 +159,8 @@ class DataParallelStep:
                 self.dist.all_reduce(p.grad)
             self.opt.step_params([p])
             return
+        if p is self.first and self.first_chunks is not None:
+            return self._issue_first_in_chunks(p)
         work = None
         side = self.side_first if p is self.first else self.side
         if self.world > 1:
@@ -161,6 +177,31 @@ class DataParallelStep:
             if ev is None:
                 ev = self.events[id(p)] = torch.cuda.Event()
             ev.record(side)
+
+    def _issue_first_in_chunks(self, p):
+        """All-reduce, optimiser update and forward gate of the first layer, one row range at a time."""
+        cols = p.numel() // p.size(0)
+        grad = p.grad.view(p.size(0), cols)
+        p.grad.record_stream(self.side_first)
+        works = [self.dist.all_reduce(grad[r0:r1], op=self.avg, group=self.urgent, async_op=True)
+                 for r0, r1, _ in self.first_chunks]
+        with torch.cuda.stream(self.side_first):
+            for (r0, r1, ev), work in zip(self.first_chunks, works):
+                work.wait()                       # stream-side wait: the host does not block
+                self.opt.step_rows(p, r0, r1 - r0, grad[r0:r1])
+                ev.record(self.side_first)
+            done = self.events.get(id(p))
+            if done is None:
+                done = self.events[id(p)] = torch.cuda.Event()
+            done.record(self.side_first)
+        if math.isinf(get_p_norm(self.net) or 0.0):
+            # p = inf: the forward of this layer waits range by range (norm_dist.DistF), not for the whole
+            # parameter; at finite p (other kernels) it waits for the event of the last range like any layer
+            _row_gates[p.data_ptr()] = [(r0, r1, ev) for r0, r1, ev in self.first_chunks]
+            self.gated = id(p)
+        else:
+            _row_gates.pop(p.data_ptr(), None)
+            self.gated = None
 
     def _on_grad(self, p):
         nbytes = p.grad.numel() * p.grad.element_size()
@@ -214,6 +255,7 @@ class DataParallelStep:
         if self.buffer_work is not None and self.cuda:
             self.buffer_work.wait()
         self.buffer_work = None
+        _row_gates.pop(self.first.data_ptr(), None)
         for h in self.handles:
             h.remove()
         self.handles = []

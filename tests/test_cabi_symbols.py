@@ -47,10 +47,12 @@ def test_error_codes_without_gpu(lib):
 
 
 def test_workspace_query(lib):
-    # 640 tiles on 444 CTA slots leave most of the second wave idle: long rows are split over k
-    assert lib.linf_inf_dist_forward_workspace_bytes(512, 5120, 5120, 1, 1) > 0
-    # fewer tiles than CTA slots: split as well
-    assert lib.linf_inf_dist_forward_workspace_bytes(64, 256, 784, 1, 1) > 0
+    # 256 tiles of 64 x 64 on 444 CTA slots, long rows: the k-tiles are dealt evenly to the CTAs, which needs scratch
+    assert lib.linf_inf_dist_forward_workspace_bytes(512, 2048, 5120, 1, 1) > 0
+    assert lib.linf_inf_dist_forward_workspace_bytes(128, 5120, 5120, 1, 1) > 0
+    # 640 tiles of 64 x 64 on 444 slots: run as 856 tiles of 64 x 48 instead, no scratch
+    assert lib.linf_inf_dist_forward_workspace_bytes(512, 5120, 5120, 1, 1) == 0
+    assert lib.linf_inf_dist_forward_workspace_bytes(512, 5120, 784, 1, 1) == 0
     # conv-shaped and tiny problems take the generic path: no scratch
     assert lib.linf_inf_dist_forward_workspace_bytes(8, 16, 27, 1, 9) == 0
     assert lib.linf_inf_dist_forward_workspace_bytes(0, 16, 27, 1, 9) == 0

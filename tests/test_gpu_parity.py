@@ -589,6 +589,29 @@ def test_inf_forward_other_loader_variants(cuda, lib, shape, variant):
         lib.linf_tune_set(0, 0)
 
 
+@pytest.mark.parametrize("shape", [(64, 64, 64, 1, 1), (33, 100, 65, 1, 1), (130, 784, 200, 1, 1), (16, 64, 256, 1, 4),
+                                   (70, 1000, 96, 1, 1), (512, 784, 640, 1, 1), (64, 3072, 512, 1, 4), (9, 36, 40, 1, 1),
+                                   (200, 256, 48, 1, 1), (65, 160, 49, 1, 1), (300, 1024, 1100, 1, 1)], ids=_ids)
+@pytest.mark.parametrize("width", [1, 2], ids=["tiles_64", "tiles_48"])
+def test_inf_forward_tile_widths(cuda, lib, shape, width):
+    """The library picks between output tiles of 64 x 64 and 64 x 48 (and k-splitting) by the shape; forced either
+    way, with and without scratch, the bits must be those of the checker -- including channel counts that are
+    no multiple of either width and grouped layers."""
+    B, CI, CO, HW, G = shape
+    x, w, _ = make_inputs(B, CI, CO, HW, G, seed=99 + CO)
+    y_ref, pos_ref = oracle.inf_dist_forward(x, w, G)
+    assert lib.linf_tune_set(5, width) == 0
+    try:
+        for split in (2, 0, 1):
+            assert lib.linf_tune_set(4, split) == 0
+            for use_ws in (False, True):
+                y, pos = c_inf_forward(dev(x), dev(w), G, use_ws=use_ws)
+                assert_bits_equal(y, y_ref, "values"); assert_bits_equal(pos, pos_ref, "arg-max")
+        assert lib.linf_tune_set(2, 0) == 0
+    finally:
+        lib.linf_tune_set(5, 0); lib.linf_tune_set(4, 0)
+
+
 def test_adamw_step_rows_equals_whole_tensor_step(cuda, lib):
     """Updating a weight matrix in row blocks, each block with moments of its own (what the sharded
     data-parallel steps do on every rank), leaves exactly the bits of one update of the whole matrix."""
@@ -790,3 +813,31 @@ def test_training_step_with_and_without_fused_mean_shift(cuda, lib):
         L.set_fused_epilogue(True)
     for qa, qb in zip(a, b):
         torch.testing.assert_close(qa, qb, rtol=1e-4, atol=1e-5)
+
+
+def test_forward_in_row_ranges_of_the_weight(cuda, lib):
+    """The data-parallel step runs the first layer's forward as one launch per row range of the weight, each
+    behind the event of that range's update.  The result (values, arg-max, gradients) must be the one of the
+    single launch."""
+    import linfdist_b200 as L
+    from linfdist_b200.norm_dist import _row_gates
+    B, CI, CO = 96, 3072, 1024
+    x, w, g = make_inputs(B, CI, CO, 1, 1, seed=4242)
+    xd = dev(x); wd = dev(w).requires_grad_(True); gd = dev(g)
+    xa = xd.clone().requires_grad_(True)
+    y0 = L.norm_dist(xa, wd, 1, float("inf"))
+    y0.backward(gd)
+    gx0, gw0 = xa.grad.clone(), wd.grad.clone()
+    wd.grad = None
+    done = torch.cuda.Event(); done.record()
+    _row_gates[wd.data_ptr()] = [(0, 256, None), (256, 512, done), (512, 768, done), (768, 1024, None)]
+    try:
+        xb = xd.clone().requires_grad_(True)
+        y1 = L.norm_dist(xb, wd, 1, float("inf"))
+        y1.backward(gd)
+    finally:
+        _row_gates.pop(wd.data_ptr(), None)
+    assert_bits_equal(y1.detach(), y0.detach(), "values")
+    assert_bits_equal(xb.grad, gx0, "grad_input"); assert_bits_equal(wd.grad, gw0, "grad_weight")
+    y_ref, _ = oracle.inf_dist_forward(x, w, 1)
+    assert_bits_equal(y1.detach(), y_ref, "values vs checker")

@@ -26,7 +26,7 @@ def _noalloc_forward(lib, x, w, G):
                                    (16, 64, 256, 1, 4), (7, 17, 10, 1, 1),
                                    # wide layers: the k-range is dealt out to every CTA slot of the GPU, so the
                                    # parked partial tiles reach (almost) the end of the library's fixed array
-                                   (512, 3072, 5120, 1, 1), (512, 5120, 5120, 1, 1), (512, 784, 2560, 1, 1)],
+                                   (512, 5120, 2048, 1, 1), (128, 5120, 5120, 1, 1), (512, 5120, 5120, 1, 1), (512, 784, 2560, 1, 1)],
                          ids=lambda s: "B{}_CI{}_CO{}_HW{}_G{}".format(*s))
 def test_noalloc_forward_matches_workspace_forward_twice(cuda, lib, shape):
     B, CI, CO, HW, G = shape
@@ -34,7 +34,7 @@ def test_noalloc_forward_matches_workspace_forward_twice(cuda, lib, shape):
     xd, wd = dev(x), dev(w)
     y_ref, pos_ref = c_inf_forward(xd, wd, G, use_ws=True)
     torch.cuda.synchronize()
-    if CI >= 3072:
+    if (B, CI, CO) in ((512, 5120, 2048), (128, 5120, 5120)):
         # these shapes must really exercise the scratch array, close to its full extent
         need = lib.linf_inf_dist_forward_workspace_bytes(B, CO, CI, G, HW)
         assert 0.8 * 30 * 1024 * 1024 <= need <= 30 * 1024 * 1024, need
