@@ -263,6 +263,38 @@ int linf_adamw_step(float* param, const float* grad, float* exp_avg, float* exp_
                     float eps, float weight_decay, int step, void* stream);
 
 /* ---------------------------------------------------------------------------------
+ * sparse gradient exchange of a data-parallel step (no counterpart in the reference, whose data
+ * parallelism is torch DistributedDataParallel, main.py:290-291: a dense all-reduce of every gradient)
+ * --------------------------------------------------------------------------------- */
+
+/*
+ * A row of an inf-dist layer's weight gradient has at most B non-zeros (every sample adds to one
+ * column).  These four calls turn the dense gradient of one rank into per-row lists, and add up the
+ * lists of all ranks, read directly from the peers' device memory (buffers that every rank can
+ * address, e.g. symmetric memory):
+ *     list of one rank:  cnt[rows] int32,  ent[rows][cap] pairs {int32 column, float value}
+ *
+ * linf_grad_rows_compact  lists the non-zeros of grad[rows, cols] in ascending column order (cnt, ent
+ *                         of THIS rank) and zeroes them in grad; a row with more than cap non-zeros
+ *                         stores 2 to *err.
+ * linf_flag_publish       stores `value` (the step number) to this rank's flag, after a system fence.
+ * linf_flags_wait         flags: device array of n pointers, one flag per rank; returns when every flag
+ *                         has reached `value`, or after timeout_ms stores 1 to *err.  Bounded; never traps.
+ * linf_grad_rows_merge    cnts / ents: device arrays of `world` pointers (rank order).  Adds, rank by
+ *                         rank, value * scale of every listed entry to grad (which compact left zero).
+ *                         Every rank adds the same numbers in the same order: identical bits on all
+ *                         ranks.  Does nothing if *err != 0.
+ * err may be device memory or mapped pinned host memory.  Call order per parameter and step, on one
+ * stream: compact, publish, wait, merge.  Use two lists per parameter alternately (odd / even steps);
+ * then the stream order of these four calls is all the synchronisation the ranks need.
+ */
+int linf_grad_rows_compact(float* grad, int rows, int cols, int cap, int* cnt, void* ent, int* err, void* stream);
+int linf_flag_publish(int* flag, int value, void* stream);
+int linf_flags_wait(const int* const* flags, int n, int value, int timeout_ms, int* err, void* stream);
+int linf_grad_rows_merge(float* grad, int rows, int cols, int cap, const int* const* cnts, const void* const* ents,
+                         int world, float scale, const int* err, void* stream);
+
+/* ---------------------------------------------------------------------------------
  * tuning hook (benchmarks and tests only; no counterpart in the reference)
  * --------------------------------------------------------------------------------- */
 

@@ -6,7 +6,7 @@ import subprocess
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "liblinfdist.so")
 CSRC = os.path.join(_HERE, "csrc")
-SOURCES = ["adamw.cu", "api.cu", "epilogue.cu", "inf_forward.cu", "inf_bound.cu", "inf_backward.cu", "inf_backward_accum.cu", "inf_backward_direct.cu", "lp.cu", "lp_tiled.cu", "no_alloc.cu", "skinny.cu"]
+SOURCES = ["adamw.cu", "api.cu", "epilogue.cu", "sparse_exchange.cu", "inf_forward.cu", "inf_bound.cu", "inf_backward.cu", "inf_backward_accum.cu", "inf_backward_direct.cu", "lp.cu", "lp_tiled.cu", "no_alloc.cu", "skinny.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "--shared", "-Xcompiler", "-fPIC"]
 
@@ -26,6 +26,10 @@ _PROTOS = {
     "linf_inf_dist_forward_post": [_F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F, _INT, _F, _F, ctypes.c_size_t, _F],
     "linf_inf_dist_bound_forward_post": [_F, _F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F, _INT, _F, _F, _F],
     "linf_mean_shift": [_F, _INT, _INT, _F, ctypes.c_float, _F, _F, _F],
+    "linf_grad_rows_compact": [_F, _INT, _INT, _INT, _F, _F, _F, _F],
+    "linf_flag_publish": [_F, _INT, _F],
+    "linf_flags_wait": [_F, _INT, _INT, _INT, _F, _F],
+    "linf_grad_rows_merge": [_F, _INT, _INT, _INT, _F, _F, _INT, ctypes.c_float, _F, _F],
     "linf_inf_dist_backward_input": [_F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F],
     "linf_inf_dist_backward_weight": [_F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F],
     "linf_inf_dist_backward": [_F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F, _F],

@@ -191,6 +191,30 @@ int linf_mean_shift(const float* input, int rows, int cols, float* running_mean,
     return mean_shift(input, rows, cols, running_mean, momentum, output, mean_out, as_stream(stream));
 }
 
+int linf_grad_rows_compact(float* grad, int rows, int cols, int cap, int* cnt, void* ent, int* err, void* stream) {
+    if (!grad || !cnt || !ent || !err) return LINF_ERR_NULL;
+    if (rows <= 0 || cols <= 0 || cap <= 0 || (long long)rows * cap > 0x7fffffffLL) return LINF_ERR_DIMS;
+    return grad_rows_compact(grad, rows, cols, cap, cnt, ent, err, as_stream(stream));
+}
+
+int linf_flag_publish(int* flag, int value, void* stream) {
+    if (!flag) return LINF_ERR_NULL;
+    return flag_publish(flag, value, as_stream(stream));
+}
+
+int linf_flags_wait(const int* const* flags, int n, int value, int timeout_ms, int* err, void* stream) {
+    if (!flags || !err) return LINF_ERR_NULL;
+    if (n <= 0 || n > 1024 || timeout_ms <= 0) return LINF_ERR_DIMS;
+    return flags_wait(flags, n, value, timeout_ms, err, as_stream(stream));
+}
+
+int linf_grad_rows_merge(float* grad, int rows, int cols, int cap, const int* const* cnts, const void* const* ents,
+                         int world, float scale, const int* err, void* stream) {
+    if (!grad || !cnts || !ents || !err) return LINF_ERR_NULL;
+    if (rows <= 0 || cols <= 0 || cap <= 0 || world <= 0 || (long long)rows * cap > 0x7fffffffLL) return LINF_ERR_DIMS;
+    return grad_rows_merge(grad, rows, cols, cap, cnts, ents, world, scale, err, as_stream(stream));
+}
+
 int linf_inf_dist_backward_input(const float* grad_output, const int* pos, int B, int CO, int CI, int G, int HW,
                                  float* grad_input, void* stream) {
     if (!grad_output || !pos || !grad_input) return LINF_ERR_NULL;

@@ -120,6 +120,12 @@ size_t inf_forward_workspace(const Dims& d);
 int inf_bound(const float* xl, const float* xu, const float* w, const Dims& d,
               float* yl, float* yu, cudaStream_t st, const Post& post = Post{nullptr, nullptr, 0});
 // batch-mean shift of a [rows, cols] activation (epilogue.cu)
+// sparse_exchange.cu: row lists of a sparse gradient, merged across ranks over peer memory
+int grad_rows_compact(float* grad, int rows, int cols, int cap, int* cnt, void* ent, int* err, cudaStream_t st);
+int flag_publish(int* flag, int value, cudaStream_t st);
+int flags_wait(const int* const* flags, int n, int value, int timeout_ms, int* err, cudaStream_t st);
+int grad_rows_merge(float* grad, int rows, int cols, int cap, const int* const* cnts, const void* const* ents,
+                    int world, float scale, const int* err, cudaStream_t st);
 int mean_shift(const float* in, int rows, int cols, float* running_mean, float momentum, float* out,
                float* mean_out, cudaStream_t st);
 int inf_backward_input(const float* g, const int* pos, const Dims& d, float* gx, cudaStream_t st);

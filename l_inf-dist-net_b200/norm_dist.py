@@ -21,11 +21,6 @@ from . import _lib
 
 _backward_mode = "ordered"
 _workspaces = {}
-# weight.data_ptr() -> [(row0, row1, event or None), ...]: a dense p = inf forward of that weight is run
-# as one launch per row range of the weight (= column range of the output), each behind its event.  Set by
-# the data-parallel training step for the first layer, whose rows are updated range by range as their
-# gradient all-reduce lands (train_step.DataParallelStep).
-_row_gates = {}
 
 
 def set_backward_mode(mode):
@@ -106,30 +101,7 @@ class DistF(torch.autograd.Function):
         B, CO, CI, G, HW = _shape5(xk, weight, group)
         y = torch.empty(B, CO, HW, device=x.device, dtype=torch.float32)
         with torch.cuda.device(x.device):
-            gates = _row_gates.get(weight.data_ptr()) if (math.isinf(p) and G == 1 and HW == 1) else None
-            if gates is not None and gates[-1][1] == CO and weight.is_contiguous():
-                # row range by row range of the weight, each as soon as that range has been updated
-                cur = torch.cuda.current_stream()
-                ys, poss = [], []
-                for r0, r1, ev in gates:
-                    if ev is not None:
-                        cur.wait_event(ev)
-                    wc = weight[r0:r1]
-                    yc = torch.empty(B, r1 - r0, HW, device=x.device, dtype=torch.float32)
-                    pc = torch.empty(B, r1 - r0, HW, device=x.device, dtype=torch.int32)
-                    need = lib.linf_inf_dist_forward_workspace_bytes(B, r1 - r0, CI, G, HW)
-                    if need:
-                        ws = _workspace(x.device, need)
-                        rc = lib.linf_inf_dist_forward_ws(xk.data_ptr(), wc.data_ptr(), B, r1 - r0, CI, G, HW,
-                                                          yc.data_ptr(), pc.data_ptr(), ws.data_ptr(), ws.numel(), _stream())
-                    else:
-                        rc = lib.linf_inf_dist_forward(xk.data_ptr(), wc.data_ptr(), B, r1 - r0, CI, G, HW,
-                                                       yc.data_ptr(), pc.data_ptr(), _stream())
-                    _lib.check(rc, "inf_dist_forward")
-                    ys.append(yc); poss.append(pc)
-                y = torch.cat(ys, dim=1); pos = torch.cat(poss, dim=1)
-                ctx.save_for_backward(xk, weight, y, pos)
-            elif math.isinf(p):
+            if math.isinf(p):
                 pos = torch.empty(B, CO, HW, device=x.device, dtype=torch.int32)
                 need = lib.linf_inf_dist_forward_workspace_bytes(B, CO, CI, G, HW)
                 if need:

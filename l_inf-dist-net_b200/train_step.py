@@ -12,7 +12,7 @@ from . import _lib
 from .adamw import AdamW
 from .bound_module import BoundFinalIdentity, Predictor
 from .nets import MLP, MLPFeature, Model
-from .norm_dist import NormDistConv, get_p_norm, set_p_norm, _row_gates
+from .norm_dist import NormDistConv, get_p_norm, set_p_norm
 
 
 def hinge(mix=0.75):
@@ -75,8 +75,6 @@ class DataParallelStep:
     averaged gradient before its next use); only the order of launches differs.  With one rank
     there is no communication and the same schedule overlaps the optimiser with the passes."""
 
-    FIRST_CHUNKS = 4      # row ranges the first layer's weight is exchanged, updated and run in
-
     def __init__(self, net, optimizer, eager_bytes=None, urgent_group=True):
         import torch.distributed as dist
         self.net, self.opt = net, optimizer
@@ -113,16 +111,6 @@ class DataParallelStep:
                 for b in self.buffers:
                     b.data = self.flat_buffers[off:off + b.numel()].view_as(b)
                     off += b.numel()
-        # ... and in row ranges: the all-reduce of range c, the optimiser on range c, and the part of the
-        # next forward that needs range c (a column range of the layer's output) form a pipeline, so that
-        # only the first range's exchange is exposed (norm_dist._row_gates; dense p = inf layers only).
-        self.first_chunks = None
-        if self.urgent is not None and self.first.dim() >= 2 and self.first.size(0) % (64 * self.FIRST_CHUNKS) == 0:
-            owner = next((m for m in net.modules() if isinstance(m, NormDistConv) and m.weight is self.first), None)
-            if owner is not None and owner.kernel_size == 1 and owner.group == 1 and self.first.is_contiguous():
-                n = self.first.size(0) // self.FIRST_CHUNKS
-                self.first_chunks = [(c * n, (c + 1) * n, torch.cuda.Event()) for c in range(self.FIRST_CHUNKS)]
-        self.gated = None               # id of the parameter whose forward waits through norm_dist._row_gates
         self.events = {}
         self.trace = None               # set to a list to record, per waiting layer, how long the forward stalled
         self.sent, self.held = 0, []
@@ -142,10 +130,8 @@ class DataParallelStep:
                 marks[0].record(cur)
             for q in own:
                 ev = self.events.get(id(q))
-                if ev is not None and id(q) != self.gated:
+                if ev is not None:
                     cur.wait_event(ev)
-                elif ev is not None:
-                    cur.wait_event(self.first_chunks[0][2])     # the later ranges are waited for inside the operator
             if marks is not None:
                 marks[1].record(cur)
                 self.trace.append((type(module).__name__ + str(tuple(own[0].shape)), marks))
@@ -159,8 +145,6 @@ class DataParallelStep:
                 self.dist.all_reduce(p.grad)
             self.opt.step_params([p])
             return
-        if p is self.first and self.first_chunks is not None:
-            return self._issue_first_in_chunks(p)
         work = None
         side = self.side_first if p is self.first else self.side
         if self.world > 1:
@@ -177,31 +161,6 @@ class DataParallelStep:
             if ev is None:
                 ev = self.events[id(p)] = torch.cuda.Event()
             ev.record(side)
-
-    def _issue_first_in_chunks(self, p):
-        """All-reduce, optimiser update and forward gate of the first layer, one row range at a time."""
-        cols = p.numel() // p.size(0)
-        grad = p.grad.view(p.size(0), cols)
-        p.grad.record_stream(self.side_first)
-        works = [self.dist.all_reduce(grad[r0:r1], op=self.avg, group=self.urgent, async_op=True)
-                 for r0, r1, _ in self.first_chunks]
-        with torch.cuda.stream(self.side_first):
-            for (r0, r1, ev), work in zip(self.first_chunks, works):
-                work.wait()                       # stream-side wait: the host does not block
-                self.opt.step_rows(p, r0, r1 - r0, grad[r0:r1])
-                ev.record(self.side_first)
-            done = self.events.get(id(p))
-            if done is None:
-                done = self.events[id(p)] = torch.cuda.Event()
-            done.record(self.side_first)
-        if math.isinf(get_p_norm(self.net) or 0.0):
-            # p = inf: the forward of this layer waits range by range (norm_dist.DistF), not for the whole
-            # parameter; at finite p (other kernels) it waits for the event of the last range like any layer
-            _row_gates[p.data_ptr()] = [(r0, r1, ev) for r0, r1, ev in self.first_chunks]
-            self.gated = id(p)
-        else:
-            _row_gates.pop(p.data_ptr(), None)
-            self.gated = None
 
     def _on_grad(self, p):
         nbytes = p.grad.numel() * p.grad.element_size()
@@ -255,10 +214,142 @@ class DataParallelStep:
         if self.buffer_work is not None and self.cuda:
             self.buffer_work.wait()
         self.buffer_work = None
-        _row_gates.pop(self.first.data_ptr(), None)
         for h in self.handles:
             h.remove()
         self.handles = []
+
+
+class SparseRowsStep(DataParallelStep):
+    """Data-parallel step whose p = inf distance layers exchange their gradients as lists of non-zeros,
+    read from the peers' memory by a kernel -- no collective, no dense traffic.
+
+    A row of an inf-dist weight gradient has at most B non-zeros (every sample adds to ONE column,
+    model/inf_dist_cuda.cu:158-171); in the CIFAR-shape step the five weight gradients together hold a
+    few hundred non-zeros in 94 M cells, and the reference's DistributedDataParallel (main.py:290-291)
+    all-reduces all 378 MB of them.  Here, per weight and on a side stream behind its gradient:
+    linf_grad_rows_compact lists the non-zeros of this rank's rows into symmetric memory (and leaves the
+    dense gradient zero), linf_flag_publish raises this rank's flag to the step number, linf_flags_wait
+    waits (bounded) for every rank's flag, linf_grad_rows_merge adds value / W of every rank's entries,
+    rank by rank, into the dense gradient, and the fused optimiser runs on it.  Every rank adds the same
+    numbers in the same order, so the replicas stay bit-identical; for a power-of-two W the result is the
+    average an all-reduce gives.  Two lists per weight are used alternately, which makes the stream
+    order of the four calls all the synchronisation the ranks need (csrc/sparse_exchange.cu).
+
+    Everything else -- biases, the dense head of the '++' nets, every parameter while p is finite (dense
+    gradients) -- takes the all-reduce of the base class.  A wait that runs out (a rank that died or
+    fell more than TIMEOUT_MS behind) sets an error word instead of hanging; it is looked at, without
+    blocking, at the start of every later step and in synchronize(), and raises there."""
+
+    TIMEOUT_MS = 30000
+
+    def __init__(self, net, optimizer):
+        super().__init__(net, optimizer)
+        if not (self.cuda and self.world > 1):
+            raise RuntimeError("SparseRowsStep needs CUDA tensors and more than one rank")
+        import os
+        import torch.distributed._symmetric_memory as symm_mem
+        self.symm = symm_mem
+        self.lib = _lib.load()
+        self.rank = self.dist.get_rank()
+        self.timeout_ms = int(os.environ.get("LINF_EXCHANGE_TIMEOUT_MS", self.TIMEOUT_MS))
+        dev = self.first.device
+        self.err = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.err_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.step_no = 0
+        self.batch = 0
+        self.lists = {}
+        dense = {id(m.weight) for m in net.modules()
+                 if isinstance(m, NormDistConv) and m.kernel_size == 1 and m.weight.requires_grad}
+        self.sparse_ok = {id(p) for p in self.params if id(p) in dense and p.is_contiguous()}
+        # symmetric memory works on this system?  (one small allocation now, so that a system without it
+        # fails here, where the caller can still fall back to the all-reduce)
+        try:
+            probe = symm_mem.empty(4, dtype=torch.int32, device=dev)
+            symm_mem.rendezvous(probe, self.dist.group.WORLD.group_name)
+        except Exception:
+            self.close()                     # take the hooks of the base class off again
+            raise
+
+    def _make_lists(self, p, cap):
+        """Two lists (odd / even steps) of `cap` entries per row in symmetric memory, and the device
+        arrays of every rank's pointers to them.  Collective: every rank gets here for the same
+        parameter at the same step."""
+        rows, W, dev = p.size(0), self.world, p.device
+        group = self.dist.group.WORLD.group_name
+        cnt = self.symm.empty(2 * rows, dtype=torch.int32, device=dev)
+        ent = self.symm.empty(2 * rows * cap * 2, dtype=torch.int32, device=dev)
+        flag = self.symm.empty(2, dtype=torch.int32, device=dev)
+        hc, he, hf = (self.symm.rendezvous(t, group) for t in (cnt, ent, flag))
+        flag.zero_()
+        torch.cuda.synchronize(dev)
+        self.dist.barrier()                  # nobody polls a flag that still holds leftovers
+        st = {"cap": cap, "cnt": cnt, "ent": ent, "flag": flag, "keep": (hc, he, hf)}
+        peers_c = [hc.get_buffer(q, (2, rows), torch.int32) for q in range(W)]
+        peers_e = [he.get_buffer(q, (2, rows * cap * 2), torch.int32) for q in range(W)]
+        peers_f = [hf.get_buffer(q, (2,), torch.int32) for q in range(W)]
+        st["peers"] = (peers_c, peers_e, peers_f)
+        for par in (0, 1):
+            st[f"cnts{par}"] = torch.tensor([t[par].data_ptr() for t in peers_c], dtype=torch.int64, device=dev)
+            st[f"ents{par}"] = torch.tensor([t[par].data_ptr() for t in peers_e], dtype=torch.int64, device=dev)
+            st[f"flags{par}"] = torch.tensor([t[par:].data_ptr() for t in peers_f], dtype=torch.int64, device=dev)
+        return st
+
+    def _issue(self, p):
+        if id(p) not in self.sparse_ok or not math.isinf(get_p_norm(self.net) or 0.0) or self.batch <= 0:
+            return super()._issue(p)
+        st = self.lists.get(id(p))
+        if st is None or st["cap"] < self.batch:
+            st = self.lists[id(p)] = self._make_lists(p, self.batch)
+        rows, cols, cap, W = p.size(0), p.numel() // p.size(0), st["cap"], self.world
+        par, lib = self.step_no & 1, self.lib
+        side = self.side_first if p is self.first else self.side
+        side.wait_stream(torch.cuda.current_stream())
+        grad = p.grad
+        if not grad.is_contiguous():
+            return super()._issue(p)
+        grad.record_stream(side)
+        with torch.cuda.stream(side):
+            s, err = side.cuda_stream, self.err.data_ptr()
+            mine_c, mine_e = st["cnt"].view(2, rows)[par], st["ent"].view(2, rows * cap * 2)[par]
+            _lib.check(lib.linf_grad_rows_compact(grad.data_ptr(), rows, cols, cap, mine_c.data_ptr(),
+                                                  mine_e.data_ptr(), err, s), "grad_rows_compact")
+            _lib.check(lib.linf_flag_publish(st["flag"][par:].data_ptr(), self.step_no, s), "flag_publish")
+            _lib.check(lib.linf_flags_wait(st[f"flags{par}"].data_ptr(), W, self.step_no, self.timeout_ms, err, s),
+                       "flags_wait")
+            _lib.check(lib.linf_grad_rows_merge(grad.data_ptr(), rows, cols, cap, st[f"cnts{par}"].data_ptr(),
+                                                st[f"ents{par}"].data_ptr(), W, 1.0 / W, err, s), "grad_rows_merge")
+            self.opt.step_params([p])
+            ev = self.events.get(id(p))
+            if ev is None:
+                ev = self.events[id(p)] = torch.cuda.Event()
+            ev.record(side)
+
+    def _check(self, wait=False):
+        if wait:
+            self.err_host.copy_(self.err)
+        code = int(self.err_host[0])
+        if code:
+            raise RuntimeError("sparse gradient exchange failed: " +
+                               ("a rank did not publish its gradient lists in time" if code == 1 else
+                                "a gradient row holds more non-zeros than the batch size allows"))
+
+    def __call__(self, *a, **k):
+        self._check()
+        if self.net.training:
+            self.step_no += 1
+            self.batch = int(a[0].size(0)) if a and torch.is_tensor(a[0]) else 0
+        return super().__call__(*a, **k)
+
+    def finish_step(self):
+        super().finish_step()
+        with torch.cuda.stream(self.side):
+            self.side.wait_stream(self.side_first)
+            self.err_host.copy_(self.err, non_blocking=True)      # looked at when the next step starts
+
+    def synchronize(self):
+        super().synchronize()
+        torch.cuda.current_stream().synchronize()
+        self._check(wait=True)
 
 
 class ShardedNcclStep(DataParallelStep):
@@ -328,16 +419,25 @@ def bench_train_step(device, world, rank, steps=8, warmup=3, batch=None, p=float
         side, classes = 64, 200
         what = ("MLPFeature 12288-5120x5 + head 5120-512(tanh)-200, MeanNorm, eps 1/255, cross entropy, "
                 "fused AdamW lr .04 wd 5e-3")
-    exchange = ("LINF_EXCHANGE=allreduce: one NCCL all-reduce (avg) per parameter issued as its gradient is ready (the first layer's on a "
-                "communicator of its own, so that it does not queue behind the others), fused optimiser per parameter as it arrives")
+    dense = ("one NCCL all-reduce (avg) per parameter issued as its gradient is ready (the first layer's on a communicator of "
+             "its own, so that it does not queue behind the others), fused optimiser per parameter as it arrives")
+    exchange = "LINF_EXCHANGE=allreduce: " + dense
     model = None
     if world > 1 and device.type == "cuda":
         import os
-        kind = os.environ.get("LINF_EXCHANGE", "allreduce")
+        kind = os.environ.get("LINF_EXCHANGE", "sparse" if math.isinf(p) else "allreduce")
         if kind == "sharded":
             model = ShardedNcclStep(net, opt)
             exchange = ("LINF_EXCHANGE=sharded: per weight matrix a NCCL reduce-scatter (avg) as its gradient is ready, the fused optimiser on this "
                         "rank's rows only, a NCCL all-gather of the updated rows; biases by all-reduce")
+        elif kind == "sparse":
+            try:
+                model = SparseRowsStep(net, opt)
+                exchange = ("LINF_EXCHANGE=sparse: the weight gradient of every p = inf distance layer travels as per-row lists of its "
+                            "non-zeros in symmetric memory, read from every peer over NVLink and added in rank order by one kernel "
+                            "per weight (no collective, no dense traffic); other parameters: " + dense)
+            except Exception as exc:           # no symmetric memory on this system
+                exchange = f"LINF_EXCHANGE=allreduce (sparse unavailable: {type(exc).__name__}): " + dense
     if model is None:
         model = DataParallelStep(net, opt)
     gen = torch.Generator().manual_seed(4040 + rank)

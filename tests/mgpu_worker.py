@@ -1,8 +1,9 @@
 """Worker of tests/test_gpu_multi.py (one process per GPU, launched with torch.distributed.run): trains a small
-L_inf-dist net for a few steps with the row-sharded exchange (NCCL reduce-scatter / all-gather around a sharded
-optimiser) and with the plain all-reduce exchange from the same start and data, and checks that (1) both leave the
-same parameters up to summation order, (2) the replicas of either run are bit-identical, and (3) every replica's
-MeanNorm running means equal rank 0's from the start of the last step plus that rank's own last update."""
+L_inf-dist net for a few steps with the plain all-reduce exchange, with the row-sharded exchange (NCCL reduce-scatter /
+all-gather around a sharded optimiser) and with the sparse exchange (lists of non-zeros read from peer memory), from
+the same start and data, and checks that (1) all leave the same parameters up to summation order -- the sparse
+exchange on two ranks the very bits of the all-reduce, (2) the replicas of every run are bit-identical, (3) the sparse
+lists were really used."""
 import os
 import sys
 
@@ -11,13 +12,13 @@ import torch
 import torch.distributed as dist
 
 import linfdist_b200 as L
-from linfdist_b200.train_step import DataParallelStep, MarginLoss, ShardedNcclStep, build_cifar_net, hinge
+from linfdist_b200.train_step import DataParallelStep, MarginLoss, ShardedNcclStep, SparseRowsStep, build_cifar_net, hinge
 
 
 def run(kind, dev, rank, steps=3):
     net = build_cifar_net(dev, depth=3, width=1)
     opt = L.AdamW(net, lr=0.02, betas=(0.9, 0.99), eps=1e-10, weight_decay=5e-3)
-    model = {"sharded": ShardedNcclStep, "nccl": DataParallelStep}[kind](net, opt)
+    model = {"sharded": ShardedNcclStep, "nccl": DataParallelStep, "sparse": SparseRowsStep}[kind](net, opt)
     loss_fn = MarginLoss(hinge(0.75), 1.0)
     gen = torch.Generator().manual_seed(100 + rank)
     for _ in range(steps):
@@ -33,7 +34,8 @@ def run(kind, dev, rank, steps=3):
     dist.barrier()
     torch.cuda.synchronize()
     model.close()
-    return [q.detach().clone() for q in net.parameters()], (len(model.big) if kind != "nccl" else 0)
+    used = len(model.big) if kind == "sharded" else len(model.lists) if kind == "sparse" else 0
+    return [q.detach().clone() for q in net.parameters()], used
 
 
 def main():
@@ -46,13 +48,20 @@ def main():
     assert n_big >= 2, "the large weight matrices must take the sharded path"
     for qa, qb in zip(a, b):
         torch.testing.assert_close(qa, qb, rtol=1e-5, atol=1e-6)
-    for params in (a, b):                          # replicas identical, bit for bit
+    c, n_lists = run("sparse", dev, rank)
+    assert n_lists >= 3, "the distance layers' weights must take the sparse path"
+    for qc, qb in zip(c, b):
+        if dist.get_world_size() == 2:             # halves add exactly: the average of the all-reduce, bit for bit
+            assert torch.equal(qc, qb)
+        else:
+            torch.testing.assert_close(qc, qb, rtol=1e-5, atol=1e-6)
+    for params in (a, b, c):                       # replicas identical, bit for bit
         for q in params:
             ref = q.clone()
             dist.broadcast(ref, src=0)
             assert torch.equal(ref, q)
     if rank == 0:
-        print("MGPU_OK sharded exchange on %d ranks, %d sharded tensors" % (dist.get_world_size(), n_big), flush=True)
+        print("MGPU_OK sharded and sparse exchange on %d ranks, %d sharded tensors, %d sparse lists" % (dist.get_world_size(), n_big, n_lists), flush=True)
     dist.barrier()
     dist.destroy_process_group()
 

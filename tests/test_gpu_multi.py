@@ -10,7 +10,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def test_sharded_exchange_matches_allreduce_exchange():
+def test_sharded_and_sparse_exchange_match_allreduce_exchange():
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     here = os.path.dirname(os.path.abspath(__file__))

@@ -813,31 +813,3 @@ def test_training_step_with_and_without_fused_mean_shift(cuda, lib):
         L.set_fused_epilogue(True)
     for qa, qb in zip(a, b):
         torch.testing.assert_close(qa, qb, rtol=1e-4, atol=1e-5)
-
-
-def test_forward_in_row_ranges_of_the_weight(cuda, lib):
-    """The data-parallel step runs the first layer's forward as one launch per row range of the weight, each
-    behind the event of that range's update.  The result (values, arg-max, gradients) must be the one of the
-    single launch."""
-    import linfdist_b200 as L
-    from linfdist_b200.norm_dist import _row_gates
-    B, CI, CO = 96, 3072, 1024
-    x, w, g = make_inputs(B, CI, CO, 1, 1, seed=4242)
-    xd = dev(x); wd = dev(w).requires_grad_(True); gd = dev(g)
-    xa = xd.clone().requires_grad_(True)
-    y0 = L.norm_dist(xa, wd, 1, float("inf"))
-    y0.backward(gd)
-    gx0, gw0 = xa.grad.clone(), wd.grad.clone()
-    wd.grad = None
-    done = torch.cuda.Event(); done.record()
-    _row_gates[wd.data_ptr()] = [(0, 256, None), (256, 512, done), (512, 768, done), (768, 1024, None)]
-    try:
-        xb = xd.clone().requires_grad_(True)
-        y1 = L.norm_dist(xb, wd, 1, float("inf"))
-        y1.backward(gd)
-    finally:
-        _row_gates.pop(wd.data_ptr(), None)
-    assert_bits_equal(y1.detach(), y0.detach(), "values")
-    assert_bits_equal(xb.grad, gx0, "grad_input"); assert_bits_equal(wd.grad, gw0, "grad_weight")
-    y_ref, _ = oracle.inf_dist_forward(x, w, 1)
-    assert_bits_equal(y1.detach(), y_ref, "values vs checker")
