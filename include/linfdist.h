@@ -308,9 +308,17 @@ int linf_grad_rows_merge(float* grad, int rows, int cols, int cap, const int* co
  *   key 4  k-splitting of the forward: 0 = by shape (default), 1 = whenever scratch is given, 2 = never
  *   key 5  width of the forward's output tiles: 0 = by shape (default), 1 = 64 columns, 2 = 48 columns wherever
  *          that kernel applies
+ *   key 6  the same for the finite-p forward
  * Returns LINF_OK, the answer of key 2, or LINF_ERR_DIMS for an unknown key / value.
  */
 int linf_tune_set(int key, int value);
+
+/*
+ * Number of CUDA kernels this library has launched in this process since it was loaded (all devices, all
+ * threads).  Diagnostics: a caller that wants to know that its step really ran on the library's kernels
+ * reads it before and after.  No counterpart in the reference.
+ */
+unsigned long long linf_launch_count(void);
 
 #ifdef __cplusplus
 }

@@ -16,6 +16,7 @@ _INT = ctypes.c_int
 # name -> argument types (return type is int unless listed in _RESTYPE)
 _PROTOS = {
     "linf_version": [],
+    "linf_launch_count": [],
     "linf_error_string": [_INT],
     "linf_tune_set": [_INT, _INT],
     "linf_inf_dist_forward": [_F, _F, _INT, _INT, _INT, _INT, _INT, _F, _F, _F],
@@ -42,6 +43,7 @@ _PROTOS = {
 }
 _RESTYPE = {
     "linf_error_string": ctypes.c_char_p,
+    "linf_launch_count": ctypes.c_ulonglong,
     "linf_inf_dist_forward_workspace_bytes": ctypes.c_size_t,
 }
 # the symbols include/linfdist.h declares

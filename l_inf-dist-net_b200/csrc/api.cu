@@ -80,10 +80,13 @@ int SideLease::join(cudaStream_t into) {
     return LINF_OK;
 }
 
+std::atomic<unsigned long long> g_launches{0};
+
 extern int inf_forward_variant;
 extern int inf_forward_tail;
 extern int inf_forward_split;
 extern int inf_forward_width;
+extern int lp_forward_width;
 int inf_forward_tma_gave_up();
 
 }  // namespace linf
@@ -98,6 +101,8 @@ inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s
 extern "C" {
 
 int linf_version(void) { return 100; }
+
+unsigned long long linf_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 const char* linf_error_string(int code) {
     switch (code) {
@@ -122,6 +127,7 @@ int linf_tune_set(int key, int value) {
     if (key == 3 && (value == 0 || value == 1)) { inf_backward_path = value; return LINF_OK; }
     if (key == 4 && value >= 0 && value <= 2) { inf_forward_split = value; return LINF_OK; }
     if (key == 5 && value >= 0 && value <= 2) { inf_forward_width = value; return LINF_OK; }
+    if (key == 6 && value >= 0 && value <= 2) { lp_forward_width = value; return LINF_OK; }
     if (key == 2) return inf_forward_tma_gave_up();   // 1 = a bounded wait of the TMA loader ran out since the library was loaded
     return LINF_ERR_DIMS;
 }

@@ -5,6 +5,8 @@
 #include <stdint.h>
 #include <stddef.h>
 
+#include <atomic>
+
 #include "../../include/linfdist.h"
 
 namespace linf {
@@ -31,7 +33,11 @@ inline int make_dims(int B, int CO, int CI, int G, int HW, Dims* d) {
     return LINF_OK;
 }
 
-inline int launch_status() {
+// Kernel launches of this library in this process (linf_launch_count): every launcher ends in launch_status.
+extern std::atomic<unsigned long long> g_launches;
+
+inline int launch_status(int launched = 1) {
+    g_launches.fetch_add((unsigned long long)launched, std::memory_order_relaxed);
     return cudaGetLastError() == cudaSuccess ? LINF_OK : LINF_ERR_LAUNCH;
 }
 

@@ -323,11 +323,13 @@ int inf_bound(const float* xl, const float* xu, const float* w, const Dims& d,
                              SMEM_BYTES) != cudaSuccess)
         return LINF_ERR_LAUNCH;
     inf_bound_tiled_kernel<<<grid, NT, SMEM_BYTES, st>>>(p);
+    int launched = 1;
     if (p.ksplit > 1 && (post.sub != nullptr || post.add != nullptr || post.negate)) {
         const size_t n = (size_t)d.R * d.CO;
         inf_bound_post_kernel<<<2 * sm_count(), 256, 0, st>>>(yl, yu, n, d.CO, post);
+        launched = 2;
     }
-    return launch_status();
+    return launch_status(launched);
 }
 
 }  // namespace linf

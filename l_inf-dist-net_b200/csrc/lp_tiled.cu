@@ -98,35 +98,38 @@ struct LpParams {
 // ------------------------------------------------------------------------------------------------
 // forward: tile = 64 rows (b) x 64 outputs (o), reduce over i; x and w tiles are K-contiguous
 // ------------------------------------------------------------------------------------------------
-template <int IP>
+// TJ = output columns per thread (4: 64-wide tiles; 3: 48-wide tiles, for shapes whose 64-wide tiles
+// leave much of their last wave of CTAs idle)
+template <int IP, int TJ>
 __global__ void __launch_bounds__(NT, 3)
 lp_forward_tiled_kernel(const LpParams p) {
     extern __shared__ __align__(16) float smem[];
-    constexpr int STAGE = (TM + TN) * LDK;
+    constexpr int TNF = 16 * TJ, NO = 8 * TJ;
+    constexpr int STAGE = (TM + TNF) * LDK;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int wm = warp & 1, wn = warp >> 1, lm = lane >> 3, ln = lane & 7;
-    const int row_off = wm * 32 + lm, col_off = wn * 32 + ln;       // + 4i rows, + 8j columns
-    const int tiles_m = (p.B + TM - 1) / TM, tiles_n = (p.COg + TN - 1) / TN;
+    const int row_off = wm * 32 + lm, col_off = wn * (8 * TJ) + ln;       // + 4i rows, + 8j columns
+    const int tiles_m = (p.B + TM - 1) / TM, tiles_n = (p.COg + TNF - 1) / TNF;
     const int g = blockIdx.x / (tiles_m * tiles_n), tg = blockIdx.x % (tiles_m * tiles_n);
-    const int n0 = (tg / tiles_m) * TN, m0 = (tg % tiles_m) * TM;
+    const int n0 = (tg / tiles_m) * TNF, m0 = (tg % tiles_m) * TM;
     const float* xg = p.x + (size_t)g * p.CIg;
     const float* wg = p.w + (size_t)g * p.COg * p.CIg;
     const int KT = (p.CIg + BK - 1) / BK;
 
-    float S[32], rM[32];
+    float S[NO], rM[NO];
 #pragma unroll
     for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < TJ; ++j) {
             const int m = min(m0 + row_off + 4 * i, p.B - 1), n = min(n0 + col_off + 8 * j, p.COg - 1);
             const float M = p.y[(size_t)m * p.CO + (size_t)g * p.COg + n];
-            rM[i * 4 + j] = M > 0.f ? 1.f / M : 0.f;
-            S[i * 4 + j] = 0.f;
+            rM[i * TJ + j] = M > 0.f ? 1.f / M : 0.f;
+            S[i * TJ + j] = 0.f;
         }
     auto load = [&](int s, int kt) {
         float* st = smem + s * STAGE;
         load_tile<TM, BK, LDK>(st, xg, p.CI, m0, p.B, kt * BK, p.CIg, tid);
-        load_tile<TN, BK, LDK>(st + TM * LDK, wg, p.CIg, n0, p.COg, kt * BK, p.CIg, tid);
+        load_tile<TNF, BK, LDK>(st + TM * LDK, wg, p.CIg, n0, p.COg, kt * BK, p.CIg, tid);
     };
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) { if (s < KT) load(s, s); cp_async_commit(); }
@@ -142,24 +145,24 @@ lp_forward_tiled_kernel(const LpParams p) {
         // fetch stalls (p = 64: 6.7 ms unrolled, 4.6 ms so)
 #pragma unroll 2
         for (int k4 = 0; k4 < BK / 4; ++k4) {
-            ulonglong2 bf[4];
+            ulonglong2 bf[TJ];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) bf[j] = *reinterpret_cast<const ulonglong2*>(Bs + (8 * j) * LDK + k4 * 4);
+            for (int j = 0; j < TJ; ++j) bf[j] = *reinterpret_cast<const ulonglong2*>(Bs + (8 * j) * LDK + k4 * 4);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const ulonglong2 af = *reinterpret_cast<const ulonglong2*>(As + (4 * i) * LDK + k4 * 4);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                for (int j = 0; j < TJ; ++j) {
                     float t0, t1, t2, t3;
                     unpack_f32x2(sub_f32x2(af.x, bf[j].x), t0, t1);
                     unpack_f32x2(sub_f32x2(af.y, bf[j].y), t2, t3);
-                    const float r = rM[i * 4 + j];
-                    float s = S[i * 4 + j];
+                    const float r = rM[i * TJ + j];
+                    float s = S[i * TJ + j];
                     s += fwd_term<IP>(fabsf(t0) * r, p.q, p.pf);
                     s += fwd_term<IP>(fabsf(t1) * r, p.q, p.pf);
                     s += fwd_term<IP>(fabsf(t2) * r, p.q, p.pf);
                     s += fwd_term<IP>(fabsf(t3) * r, p.q, p.pf);
-                    S[i * 4 + j] = s;
+                    S[i * TJ + j] = s;
                 }
             }
         }
@@ -171,12 +174,12 @@ lp_forward_tiled_kernel(const LpParams p) {
     for (int i = 0; i < 8; ++i) {
         const int m = m0 + row_off + 4 * i;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < TJ; ++j) {
             const int n = n0 + col_off + 8 * j;
             if (m < p.B && n < p.COg) {
                 float* yo = p.y + (size_t)m * p.CO + (size_t)g * p.COg + n;
                 const float M = *yo;                     // still the normaliser: nobody else writes this element
-                *yo = M > 0.f ? powf(S[i * 4 + j], p.inv_p) * M : 0.f;
+                *yo = M > 0.f ? powf(S[i * TJ + j], p.inv_p) * M : 0.f;
             }
         }
     }
@@ -346,7 +349,6 @@ int set_smem(K kern, int bytes) {
                                                                                                          : LINF_ERR_LAUNCH;
 }
 
-constexpr int FWD_SMEM = STAGES * (TM + TN) * LDK * 4;
 constexpr int BWD_X_SMEM = STAGES * (2 * TM * LDK + BK * LDN) * 4;
 constexpr int BWD_W_SMEM = STAGES * (3 * BK * LDN) * 4;
 
@@ -368,13 +370,32 @@ static LpParams make_params(const float* x, const float* w, const float* g, floa
     return P;
 }
 
+int lp_forward_width = 0;   // 0: tile width by shape; 1: 64 columns; 2: 48 columns (benchmarking knob)
+
 // `y` holds max_i |x - w| on entry and the L_p distance on exit
 int lp_forward_tiled(const float* x, const float* w, const Dims& d, float* y, float p, cudaStream_t st) {
     const LpParams P = make_params(x, w, nullptr, y, nullptr, d, p, p);
-    const int grid = ((d.R + TM - 1) / TM) * ((d.COg + TN - 1) / TN) * d.G;
-#define LINF_FWD(IPV)                                                                          \
-    { if (set_smem(lp_forward_tiled_kernel<IPV>, FWD_SMEM)) return LINF_ERR_LAUNCH;            \
-      lp_forward_tiled_kernel<IPV><<<grid, NT, FWD_SMEM, st>>>(P); return launch_status(); }
+    // The kernel is bound by FP32 throughput: an SM of the last, partial wave takes a third of a full wave per CTA
+    // it holds.  48-wide tiles cost 3/4 of 64-wide ones and are taken when that buys a shorter launch
+    // (B = 512, Dout = 5120: 640 tiles on 444 slots = 1 + 2/3 waves, against 856 tiles = 2 x 3/4).
+    const int tiles_m = (d.R + TM - 1) / TM, slots = 3 * sm_count(), sms = sm_count();
+    auto cost = [&](int tn) {
+        const int tiles = tiles_m * ((d.COg + tn - 1) / tn) * d.G, rest = tiles % slots;
+        return (tn / 64.0) * ((tiles / slots) + ((rest + sms - 1) / sms) / 3.0);
+    };
+    const bool narrow = lp_forward_width == 2 || (lp_forward_width == 0 && d.COg >= 48 && cost(48) < 0.97 * cost(64));
+    const int tn = narrow ? 48 : 64;
+    const int grid = tiles_m * ((d.COg + tn - 1) / tn) * d.G;
+    const int smem = STAGES * (TM + tn) * LDK * 4;
+#define LINF_FWD(IPV)                                                                                       \
+    { if (narrow) {                                                                                         \
+          if (set_smem(lp_forward_tiled_kernel<IPV, 3>, smem)) return LINF_ERR_LAUNCH;                      \
+          lp_forward_tiled_kernel<IPV, 3><<<grid, NT, smem, st>>>(P);                                       \
+      } else {                                                                                              \
+          if (set_smem(lp_forward_tiled_kernel<IPV, 4>, smem)) return LINF_ERR_LAUNCH;                      \
+          lp_forward_tiled_kernel<IPV, 4><<<grid, NT, smem, st>>>(P);                                       \
+      }                                                                                                     \
+      return launch_status(); }
     if (p == 8.f) LINF_FWD(8)
     if (p == 16.f) LINF_FWD(16)
     if (p == 64.f) LINF_FWD(64)

@@ -487,11 +487,13 @@ def bench_train_step(device, world, rank, steps=8, warmup=3, batch=None, p=float
     # next step's layers, so over many steps nothing is left out)
     marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
     marks[0].record()
+    launches = _lib.load().linf_launch_count()
     for k in range(steps):
         loss = step()
         if k == steps - 1:
             model.synchronize()
         marks[k + 1].record()
+    launches = _lib.load().linf_launch_count() - launches     # kernels of the library in the timed steps (this rank)
     last = float(loss.item())
     if world > 1:
         dist.barrier()
@@ -535,6 +537,7 @@ def bench_train_step(device, world, rank, steps=8, warmup=3, batch=None, p=float
     name = "CIFAR-shape L_inf-dist net" if config == "cifar" else "TinyImageNet-shape L_inf-dist net+MLP"
     return {"metric": name + " train samples/s", "value": world * batch / (ms * 1e-3),
             "unit": "samples/s", "ms_per_step": ms, "ms_per_step_mean": ms_mean, "steps": steps, "warmup": warmup,
+            "gpu_launches": int(launches),
             "timing": "median over the timed steps, CUDA events, max over ranks",
             "batch_per_gpu": batch, "n_gpus": world, "exchange": exchange if world > 1 else "none (one GPU)",
             "p": "inf" if math.isinf(p) else p, "loss": last, "parameters": params, "forward_stall": stalls,

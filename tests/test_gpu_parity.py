@@ -176,6 +176,27 @@ def test_lp_against_oracle(cuda, lib, shape, p):
     assert_lp_close(gw, gw_ref, "grad_weight", rtol=rtol)
 
 
+@pytest.mark.parametrize("shape", [(64, 128, 128, 1, 1), (40, 784, 96, 1, 1), (70, 256, 100, 1, 1), (130, 64, 52, 1, 1),
+                                   (33, 128, 192, 1, 4)], ids=_ids)
+@pytest.mark.parametrize("p", [8.0, 64.0, 11.3])
+def test_lp_forward_tile_widths(cuda, lib, shape, p):
+    """The finite-p forward picks 64- or 48-wide output tiles by the shape.  Every output is summed over the inputs
+    in the same order either way: forced to one width or the other the bits are the same, and they agree with the
+    checker."""
+    B, CI, CO, HW, G = shape
+    x, w, _ = make_inputs(B, CI, CO, HW, G, seed=1200 + CO, x_dist="normal")
+    y_ref = oracle.norm_dist_forward(x, w, G, p)
+    ys = []
+    try:
+        for width in (1, 2):
+            assert lib.linf_tune_set(6, width) == 0
+            ys.append(c_lp_forward(dev(x), dev(w), G, p))
+    finally:
+        lib.linf_tune_set(6, 0)
+    assert_bits_equal(ys[0], ys[1].cpu().numpy(), "48-wide against 64-wide tiles")
+    assert_lp_close(ys[1], y_ref, "forward, 48-wide tiles", floor=0.0)
+
+
 def test_lp_against_golden(cuda, lib):
     z = np.load(os.path.join(GOLDEN, "lp.npz"))
     cases = sorted({k.split("_")[0] for k in z.files if k.startswith("c")})
