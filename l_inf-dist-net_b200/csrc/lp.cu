@@ -95,6 +95,87 @@ lp_forward_generic_kernel(const float* __restrict__ x, const float* __restrict__
     }
 }
 
+// ---- forward for very few outputs per group (the 5120 -> 10 classifier layer) ------------------
+// The 32 x 32 tiles above would give a handful of CTAs that each walk all of K alone (2.3 ms at
+// B = 512, K = 5120, 10 outputs).  As in the inf-dist kernel for such layers the reduction dimension is
+// spread over the threads of a CTA that owns R rows: thread t walks the 16-byte chunks t, t + 256, ...
+// of those rows and of every weight row; the partial sums are added over the lanes by a butterfly and
+// over the warps in warp order (a fixed order: same bits on every run).
+template <int NMAX, int R>
+__global__ void __launch_bounds__(256)
+lp_forward_skinny_kernel(const float* __restrict__ x, const float* __restrict__ w, Dims d,
+                         float* __restrict__ y, PowPlan pl, float inv_p) {
+    __shared__ float s_s[8][R][NMAX];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpc = blockDim.x >> 5;
+    const int N = d.COg, K = d.CIg;
+    const int row_blocks = (d.R + R - 1) / R;
+    const int g = blockIdx.x / row_blocks, r0 = (blockIdx.x - g * row_blocks) * R;
+    float S[R][NMAX], rM[R][NMAX];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int n = 0; n < NMAX; ++n) {
+            const float M = (n < N) ? y[(size_t)min(r0 + r, d.R - 1) * d.CO + (size_t)g * N + n] : 0.f;
+            rM[r][n] = M > 0.f ? 1.f / M : 0.f;
+            S[r][n] = 0.f;
+        }
+    const float* xr[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) xr[r] = x + (size_t)min(r0 + r, d.R - 1) * d.CI + (size_t)g * K;
+    const float* wg = w + (size_t)g * N * K;
+    for (int k = threadIdx.x * 4; k < K; k += 4 * blockDim.x) {
+        float4 xv[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) xv[r] = __ldg(reinterpret_cast<const float4*>(xr[r] + k));
+#pragma unroll
+        for (int n = 0; n < NMAX; ++n) {
+            if (n < N) {
+                const float4 wv = __ldg(reinterpret_cast<const float4*>(wg + (size_t)n * K + k));
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const float m = rM[r][n];
+                    float a = S[r][n];
+                    a += pow_unit(fminf(fabsf(xv[r].x - wv.x) * m, 1.f), pl);
+                    a += pow_unit(fminf(fabsf(xv[r].y - wv.y) * m, 1.f), pl);
+                    a += pow_unit(fminf(fabsf(xv[r].z - wv.z) * m, 1.f), pl);
+                    a += pow_unit(fminf(fabsf(xv[r].w - wv.w) * m, 1.f), pl);
+                    S[r][n] = a;
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int n = 0; n < NMAX; ++n) {
+            if (n < N) {
+                float a = S[r][n];
+#pragma unroll
+                for (int sft = 16; sft >= 1; sft >>= 1) a += __shfl_xor_sync(0xffffffffu, a, sft);
+                if (lane == 0) s_s[warp][r][n] = a;
+            }
+        }
+    __syncthreads();
+    for (int q = threadIdx.x; q < R * NMAX; q += blockDim.x) {
+        const int r = q / NMAX, n = q % NMAX;
+        if (n < N && r0 + r < d.R) {
+            float a = s_s[0][r][n];
+            for (int wv = 1; wv < wpc; ++wv) a += s_s[wv][r][n];
+            float* yo = y + (size_t)(r0 + r) * d.CO + (size_t)g * N + n;
+            const float M = *yo;
+            *yo = M > 0.f ? powf(a, inv_p) * M : 0.f;
+        }
+    }
+}
+
+template <int NMAX, int R>
+int launch_lp_skinny(const float* x, const float* w, const Dims& d, float* y, float p, cudaStream_t st) {
+    const int items = ((d.R + R - 1) / R) * d.G;
+    const int wpc = min(8, max(1, d.CIg / 512));
+    lp_forward_skinny_kernel<NMAX, R><<<items, 32 * wpc, 0, st>>>(x, w, d, y, make_plan(p), 1.f / p);
+    return launch_status();
+}
+
 // ---- backward w.r.t. the input: tile = 32 rows x 32 input channels, loop over outputs -------
 template <bool ROW_FAST>
 __global__ void __launch_bounds__(256)
@@ -217,6 +298,12 @@ int lp_forward(const float* x, const float* w, const Dims& d, float* y, float p,
     int rc = inf_forward(x, w, d, y, nullptr, nullptr, 0, st);
     if (rc != LINF_OK) return rc;
     if (lp_tiled_ok(d, x, w, y, nullptr, nullptr)) return lp_forward_tiled(x, w, d, y, p, st);
+    if (skinny_ok(d, x, w, nullptr)) {
+        if (d.COg <= 4) return launch_lp_skinny<4, 4>(x, w, d, y, p, st);
+        if (d.COg <= 8) return launch_lp_skinny<8, 2>(x, w, d, y, p, st);
+        if (d.COg <= 16) return launch_lp_skinny<16, 2>(x, w, d, y, p, st);
+        return launch_lp_skinny<32, 1>(x, w, d, y, p, st);
+    }
     dim3 grid((d.R + GT - 1) / GT, (d.COg + GT - 1) / GT, d.G);
     if (!grid_ok(grid)) return LINF_ERR_DIMS;
     const PowPlan pl = make_plan(p);

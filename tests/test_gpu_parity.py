@@ -156,7 +156,9 @@ def test_inf_bound_irregular_inputs(cuda, lib, kind, CI):
 
 
 LP_SHAPES = [(1, 1, 1, 1, 1), (7, 17, 10, 1, 1), (3, 18, 12, 5, 3), (6, 32, 48, 1, 4),
-             (33, 100, 65, 1, 1), (64, 128, 128, 1, 1), (40, 784, 96, 1, 1)]
+             (33, 100, 65, 1, 1), (64, 128, 128, 1, 1), (40, 784, 96, 1, 1),
+             # few outputs per group, long rows: the forward spreads the reduction over a CTA
+             (70, 2048, 10, 1, 1), (33, 512, 24, 1, 2), (9, 1024, 3, 1, 1), (5, 640, 31, 1, 1)]
 
 
 @pytest.mark.parametrize("shape", LP_SHAPES, ids=_ids)
