@@ -347,7 +347,31 @@ def extra_legs(torch, lib, dev, flush, lane_peak, hbm_peak):
             entry["frac_mufu_backward"] = 2.0 * 2.0 * terms / ((t_gx + t_gw) * 1e-6) / mufu_peak
             lp[f"p{p:g}"] = entry
     out["lp"] = lp
-    del x, w, g, y, gx, gw
+
+    # ---- the inf-dist layer at the shape that dominates training (5120 -> 5120, B = 512; w, g of config 2) -----------
+    # inputs as in the headline workload: x uniform in [0, 1), w ~ N(0,1); the backward is also timed on the arg-max
+    # positions of x ~ N(0,1), where a few hundred input coordinates attract most positions of a sample
+    pos = torch.empty(Bq, CO, 1, device=dev, dtype=torch.int32)
+    need = lib.linf_inf_dist_forward_workspace_bytes(Bq, CO, CI, 1, 1)
+    ws = torch.empty(max(need, 1), dtype=torch.uint8, device=dev)
+    x_u = torch.rand(Bq, CI, 1, generator=gen).to(dev)
+    wide = {"workload": "inf-dist layer fwd+bwd fp32 G=1: B=512, Din=5120, Dout=5120 (the hidden layers of configs 4 and 5)",
+            "unit": "terms/s", "note": "2 algorithmic fp32 operations per term, as in `roofline`; the backward adds none"}
+    for tag, xin in (("uniform_x", x_u), ("normal_x", x)):
+        def wide_fwd():
+            a = (xin.data_ptr(), w.data_ptr(), Bq, CO, CI, 1, 1, y.data_ptr(), pos.data_ptr())
+            rc = (lib.linf_inf_dist_forward_ws(*a, ws.data_ptr(), need, stream) if need else lib.linf_inf_dist_forward(*a, stream))
+            _lib.check(rc, "wide forward")
+
+        t_f = _timed_us(torch, wide_fwd, flush, n=7, warm=2)
+        t_b = _timed_us(torch, lambda: _lib.check(lib.linf_inf_dist_backward(
+            g.data_ptr(), pos.data_ptr(), Bq, CO, CI, 1, 1, gx.data_ptr(), gw.data_ptr(), stream), "wide backward"), flush, n=7, warm=2)
+        wide[tag] = {"us_forward": t_f, "us_backward": t_b, "value": terms / ((t_f + t_b) * 1e-6),
+                     "frac_fp32_issue_forward": 2.0 * terms / (t_f * 1e-6) / lane_peak,
+                     "frac_fp32_issue_fwd_bwd": 2.0 * terms / ((t_f + t_b) * 1e-6) / lane_peak}
+    out["layer_wide"] = wide
+    del x_u
+    del x, w, g, y, gx, gw, pos, ws
 
     # ---- config 3: interval bounds, B = 512, Din = 3072, Dout = 5120, groups 1 and 4 ----------------
     Bq, CI, CO = 512, 3072, 5120

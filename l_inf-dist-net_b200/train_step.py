@@ -526,6 +526,24 @@ def bench_train_step(device, world, rank, steps=8, warmup=3, batch=None, p=float
             t = torch.tensor([stalls["ms_per_step"]], device=device, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             stalls["ms_per_step_max_over_ranks"] = float(t.item())
+        # Timeline of the exchange: how long after the last kernel of the backward pass the update of each
+        # parameter has landed (negative: before the backward ended).  Three more steps, each followed by a
+        # device synchronisation so that the events can be read; the timed steps above are not affected.
+        for q in model.params:
+            model.events[id(q)] = torch.cuda.Event(enable_timing=True)
+        n_lag, lag, names = 3, {}, {}
+        for k, (mname, m) in enumerate(net.named_modules()):
+            for q in m.parameters(recurse=False):
+                names[id(q)] = f"{mname}:{type(m).__name__}{tuple(q.shape)}"
+        for _ in range(n_lag):
+            step()
+            end_bwd = torch.cuda.Event(enable_timing=True)
+            end_bwd.record()
+            model.synchronize()
+            torch.cuda.synchronize()
+            for q in model.params:
+                lag[names[id(q)]] = lag.get(names[id(q)], 0.0) + end_bwd.elapsed_time(model.events[id(q)]) / n_lag
+        stalls["update_landed_ms_after_backward"] = lag
     params = sum(q.numel() for q in net.parameters())
     # give the memory of this leg back before the next one (another model in the same process)
     model.close()
