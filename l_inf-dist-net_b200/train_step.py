@@ -247,6 +247,10 @@ class SparseRowsStep(DataParallelStep):
         if not (self.cuda and self.world > 1):
             raise RuntimeError("SparseRowsStep needs CUDA tensors and more than one rank")
         import os
+        # The exchange reads the peers' lists with plain loads; it never uses multimem instructions.  Keeping the
+        # symmetric buffers off an NVLink multicast object means that a rank which dies leaves nothing bound that
+        # its peers' GPUs could fault on (PyTorch reads this switch when it sets the allocation up).
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
         self.symm = symm_mem
         self.lib = _lib.load()
