@@ -14,7 +14,7 @@ def test_sharded_and_sparse_exchange_match_allreduce_exchange():
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     here = os.path.dirname(os.path.abspath(__file__))
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
            "--master-addr", "127.0.0.1", "--master-port", "29533", os.path.join(here, "mgpu_worker.py")]
     # the launcher and its workers form a process group of their own, so that a timeout ends all of them
