@@ -304,7 +304,8 @@ int linf_grad_rows_merge(float* grad, int rows, int cols, int cap, const int* co
  *   key 0  tiled inf-dist forward variant (0 = default; the table is in csrc/inf_forward.cu)
  *   key 1  1 = run a partial last wave of output tiles as half-width tiles (default), 0 = never
  *   key 2  (value ignored) returns 1 if a bounded wait of the TMA-loader variant ever ran out, else 0
- *   key 3  1 = skip the direct-accumulation grad_input kernel, 0 = use it where it applies (default)
+ *   key 3  grad_input of dense layers: 0 = direct-accumulation or sort kernel as a probe of the positions decides
+ *          (default), 1 = never the direct kernel, 2 = the direct kernel wherever it fits, without the probe
  *   key 4  k-splitting of the forward: 0 = by shape (default), 1 = whenever scratch is given, 2 = never
  *   key 5  width of the forward's output tiles: 0 = by shape (default), 1 = 64 columns, 2 = 48 columns wherever
  *          that kernel applies

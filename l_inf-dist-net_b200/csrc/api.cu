@@ -124,7 +124,7 @@ const char* linf_error_string(int code) {
 int linf_tune_set(int key, int value) {
     if (key == 0 && value >= 0 && value < 16) { inf_forward_variant = value; return LINF_OK; }
     if (key == 1 && (value == 0 || value == 1)) { inf_forward_tail = value; return LINF_OK; }
-    if (key == 3 && (value == 0 || value == 1)) { inf_backward_path = value; return LINF_OK; }
+    if (key == 3 && value >= 0 && value <= 2) { inf_backward_path = value; return LINF_OK; }
     if (key == 4 && value >= 0 && value <= 2) { inf_forward_split = value; return LINF_OK; }
     if (key == 5 && value >= 0 && value <= 2) { inf_forward_width = value; return LINF_OK; }
     if (key == 6 && value >= 0 && value <= 2) { lp_forward_width = value; return LINF_OK; }

@@ -141,7 +141,16 @@ int inf_backward_atomic(const float* g, const int* pos, const Dims& d, float* gx
 // sort-free ordered grad_weight for dense layers (inf_backward_accum.cu); -1 = shape not taken
 int inf_backward_weight_accum(const float* g, const int* pos, const Dims& d, float* gw, cudaStream_t st);
 // direct accumulation in shared memory for dense layers (inf_backward_direct.cu); -1 = shape not taken
-int inf_backward_input_direct(const float* g, const int* pos, const Dims& d, float* gx, cudaStream_t st);
+// The verdict of the grad_input probe (inf_backward_direct.cu): one word per probed row.
+constexpr int kGxProbeRows = 8;
+__device__ __forceinline__ bool probe_says_contested(const int* __restrict__ words) {
+    int any = 0;
+#pragma unroll
+    for (int k = 0; k < kGxProbeRows; ++k) any |= words[k];
+    return any != 0;
+}
+int inf_backward_input_direct(const float* g, const int* pos, const Dims& d, float* gx, cudaStream_t st,
+                              const int** decided_by = nullptr);
 extern int inf_backward_path;
 int inf_backward_ordered_both(const float* g, const int* pos, const Dims& d, float* gx, float* gw,
                               cudaStream_t st);

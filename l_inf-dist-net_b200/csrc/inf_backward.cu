@@ -27,7 +27,8 @@
 
 namespace linf {
 
-int inf_backward_path = 0;   // benchmarking knob: 1 = skip the direct-accumulation kernels
+int inf_backward_path = 0;   // benchmarking knob: 0 = grad_input by the direct or the sort kernel as a probe of the positions decides;
+                             // 1 = never the direct kernel; 2 = the direct kernel wherever it fits, no probe
 
 namespace {
 
@@ -306,7 +307,8 @@ __host__ __device__ inline int fast_group_words(int nb, int n_src) {
 template <int MODE, int EPT>
 __global__ void __launch_bounds__(512)
 inf_backward_rows_kernel(const float* __restrict__ gout, const int* __restrict__ pos, Dims d,
-                         float* __restrict__ dst, int n_rows, int n_src) {
+                         float* __restrict__ dst, int n_rows, int n_src, const int* __restrict__ only_if) {
+    if (only_if != nullptr && !probe_says_contested(only_if)) return;     // the direct-accumulation kernel did these rows
     extern __shared__ __align__(16) int smem_i[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int GS = blockDim.x, gt = threadIdx.x;
@@ -515,12 +517,12 @@ int launch_ordered_as(const float* g, const int* pos, const Dims& d, float* dst,
 
 template <int MODE, int EPT>
 int launch_fast(const float* g, const int* pos, const Dims& d, float* dst, cudaStream_t st,
-                int n_rows, int n_src, int warps, size_t smem) {
+                int n_rows, int n_src, int warps, size_t smem, const int* only_if) {
     auto kern = inf_backward_rows_kernel<MODE, EPT>;
     if (smem > 40 * 1024 &&
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT) != cudaSuccess)
         return LINF_ERR_LAUNCH;
-    kern<<<n_rows, 32 * warps, smem, st>>>(g, pos, d, dst, n_rows, n_src);
+    kern<<<n_rows, 32 * warps, smem, st>>>(g, pos, d, dst, n_rows, n_src, only_if);
     return launch_status();
 }
 
@@ -529,32 +531,28 @@ int launch_ordered(const float* g, const int* pos, const Dims& d, float* dst, cu
     const int n_rows = (MODE == 0) ? d.R * d.G : d.CO;
     const int n_src = (MODE == 0) ? d.COg : d.R;
     const int nb = d.CIg;
+    // grad_input: the sort kernel with the sources held in registers applies whenever the row fits its thread group
+    const size_t fast_bytes = (size_t)fast_group_words(nb, n_src) * 4;
+    const bool fast_ok = MODE == 0 && n_src <= 512 * 24 && fast_bytes <= SMEM_LIMIT;
+    const int* only_if = nullptr;
     if (MODE == 0 && inf_backward_path != 1) {
-        // dense layers with many bins per source: direct accumulation (inf_backward_direct.cu)
-        int rc = inf_backward_input_direct(g, pos, d, dst, st);
-        if (rc >= 0) return rc;
+        // Dense layers with many bins per source: direct accumulation (inf_backward_direct.cu).  Where its speed
+        // depends on how the positions are spread, a probe decides between it and the sort kernel below.
+        int rc = inf_backward_input_direct(g, pos, d, dst, st, fast_ok ? &only_if : nullptr);
+        if (rc > 0 || (rc == 0 && only_if == nullptr)) return rc;
     }
     if (MODE == 1) {
         // dense layers with longer rows: the warp-per-row kernel (inf_backward_accum.cu)
         int rc = inf_backward_weight_accum(g, pos, d, dst, st);
         if (rc >= 0) return rc;
     }
-    {
-        // grad_input: fast path (sources held in registers) whenever the row fits its thread group
-        // (dense grad_weight rows were taken by the sort-free kernel above)
-        int rc = -1;
-        if (MODE == 0 && n_src <= 512 * 24) {
-            // one CTA of 16 warps per row; the smallest per-thread share that covers the row
-            const size_t gb = (size_t)fast_group_words(nb, n_src) * 4;
-            if (gb <= SMEM_LIMIT) {
-                if (n_src <= 512 * 4) rc = launch_fast<MODE, 4>(g, pos, d, dst, st, n_rows, n_src, 16, gb);
-                else if (n_src <= 512 * 8) rc = launch_fast<MODE, 8>(g, pos, d, dst, st, n_rows, n_src, 16, gb);
-                else if (n_src <= 512 * 12) rc = launch_fast<MODE, 12>(g, pos, d, dst, st, n_rows, n_src, 16, gb);
-                else if (n_src <= 512 * 16) rc = launch_fast<MODE, 16>(g, pos, d, dst, st, n_rows, n_src, 16, gb);
-                else rc = launch_fast<MODE, 24>(g, pos, d, dst, st, n_rows, n_src, 16, gb);
-            }
-        }
-        if (rc >= 0) return rc;
+    if (fast_ok) {
+        // one CTA of 16 warps per row; the smallest per-thread share that covers the row
+        if (n_src <= 512 * 4) return launch_fast<MODE, 4>(g, pos, d, dst, st, n_rows, n_src, 16, fast_bytes, only_if);
+        if (n_src <= 512 * 8) return launch_fast<MODE, 8>(g, pos, d, dst, st, n_rows, n_src, 16, fast_bytes, only_if);
+        if (n_src <= 512 * 12) return launch_fast<MODE, 12>(g, pos, d, dst, st, n_rows, n_src, 16, fast_bytes, only_if);
+        if (n_src <= 512 * 16) return launch_fast<MODE, 16>(g, pos, d, dst, st, n_rows, n_src, 16, fast_bytes, only_if);
+        return launch_fast<MODE, 24>(g, pos, d, dst, st, n_rows, n_src, 16, fast_bytes, only_if);
     }
     const bool compact = n_src < nb;                 // fewer sources than bins: go through dense ids
     if ((size_t)group_words(1, nb, n_src, compact, false, false) * 4 > SMEM_LIMIT) return LINF_ERR_TOO_LARGE;

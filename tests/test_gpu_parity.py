@@ -590,6 +590,35 @@ def test_inf_backward_synthetic_positions(cuda, lib, pattern, shape):
         assert_bits_equal(gx, gx_ref, f"{mode} grad_input"); assert_bits_equal(gw, gw_ref, f"{mode} grad_weight")
 
 
+@pytest.mark.parametrize("pattern", ["hot", "spread", "mixed"])
+def test_inf_backward_input_kernel_choice(cuda, lib, pattern):
+    """grad_input of a wide dense layer runs on the direct-accumulation kernel or on the sort kernel, as a probe of
+    the arg-max positions decides (many sources of a row in few bins: the sort).  Whatever the probe says, and with
+    either kernel forced, the bits are the checker's."""
+    B, CI, CO = 40, 2048, 1536
+    rng = np.random.default_rng(7 + len(pattern))
+    if pattern == "hot":            # three quarters of every row's sources in a dozen bins
+        idx = np.where(rng.random((B, CO, 1)) < 0.75, rng.integers(0, 12, (B, CO, 1)) * 97, rng.integers(0, CI, (B, CO, 1)))
+    elif pattern == "spread":
+        idx = rng.integers(0, CI, (B, CO, 1))
+    else:                           # only some rows are contested (the probe samples rows: either answer must be right)
+        idx = rng.integers(0, CI, (B, CO, 1))
+        idx[::5] = rng.integers(0, 3, (len(idx[::5]), CO, 1)) * 11
+    sign = rng.integers(0, 2, (B, CO, 1)).astype(np.uint32) << 31
+    pos = (idx.astype(np.uint32) | sign).view(np.int32)
+    g = rng.standard_normal((B, CO, 1)).astype(np.float32)
+    gx_ref, gw_ref = oracle.inf_dist_backward(g, pos, CI, 1)
+    try:
+        for path in (0, 1, 2):
+            assert lib.linf_tune_set(3, path) == 0
+            for mode in ("ordered", "both"):
+                gx, gw = c_inf_backward(dev(g), dev(pos), CI, 1, mode)
+                assert_bits_equal(gx, gx_ref, f"path {path} {mode} grad_input")
+                assert_bits_equal(gw, gw_ref, f"path {path} {mode} grad_weight")
+    finally:
+        lib.linf_tune_set(3, 0)
+
+
 @pytest.mark.parametrize("shape", [(64, 64, 64, 1, 1), (33, 100, 65, 1, 1), (130, 784, 200, 1, 1), (16, 64, 256, 1, 4),
                                    (70, 1000, 96, 1, 1), (512, 784, 640, 1, 1), (64, 3072, 512, 1, 4), (9, 36, 40, 1, 1)], ids=_ids)
 @pytest.mark.parametrize("variant", [4, 1, 2, 3], ids=["tma_padded", "cp_async_32", "cp_async_16", "window_16"])
