@@ -59,8 +59,9 @@ def cross_entropy():
 class DataParallelStep:
     """Training step of one model replica per GPU, scheduled by hand on top of stock
     torch.distributed collectives (no DistributedDataParallel wrapper):
-      * parameters are broadcast from rank 0 once; the MeanNorm running means are broadcast from
-        rank 0 at the start of every step (what DDP's broadcast_buffers does);
+      * parameters are broadcast from rank 0 once; the MeanNorm running means (views of one flat tensor)
+        are broadcast from rank 0 right after the forward that updated them and waited for at the start of
+        the next step: the same values at the start of every step as DDP's broadcast_buffers gives;
       * when autograd has accumulated the gradient of a parameter, its all-reduce (average) is
         issued asynchronously and, on a side stream that waits for exactly that all-reduce, the
         optimiser updates that parameter; the next forward waits, layer by layer, only for the
