@@ -243,10 +243,14 @@ class SparseRowsStep(DataParallelStep):
 
     TIMEOUT_MS = 30000
 
-    def __init__(self, net, optimizer):
+    def __init__(self, net, optimizer, row_capacity=None):
+        """row_capacity: entries a row's list can hold; default = the batch size of the first step, which is
+        the most a row can have when every weight is used once per forward pass (a net that runs a layer k
+        times per step, e.g. on value, lower and upper bound, needs k times the batch size)."""
         super().__init__(net, optimizer)
         if not (self.cuda and self.world > 1):
             raise RuntimeError("SparseRowsStep needs CUDA tensors and more than one rank")
+        self.row_capacity = row_capacity
         import os
         # The exchange reads the peers' lists with plain loads; it never uses multimem instructions.  Keeping the
         # symmetric buffers off an NVLink multicast object means that a rank which dies leaves nothing bound that
@@ -303,8 +307,9 @@ class SparseRowsStep(DataParallelStep):
         if id(p) not in self.sparse_ok or not math.isinf(get_p_norm(self.net) or 0.0) or self.batch <= 0:
             return super()._issue(p)
         st = self.lists.get(id(p))
-        if st is None or st["cap"] < self.batch:
-            st = self.lists[id(p)] = self._make_lists(p, self.batch)
+        want = self.row_capacity or self.batch
+        if st is None or st["cap"] < want:
+            st = self.lists[id(p)] = self._make_lists(p, want)
         rows, cols, cap, W = p.size(0), p.numel() // p.size(0), st["cap"], self.world
         par, lib = self.step_no & 1, self.lib
         side = self.side_first if p is self.first else self.side
@@ -336,7 +341,7 @@ class SparseRowsStep(DataParallelStep):
         if code:
             raise RuntimeError("sparse gradient exchange failed: " +
                                ("a rank did not publish its gradient lists in time" if code == 1 else
-                                "a gradient row holds more non-zeros than the batch size allows"))
+                                "a gradient row holds more non-zeros than its list has room for (row_capacity)"))
 
     def __call__(self, *a, **k):
         self._check()
