@@ -45,29 +45,37 @@ grad_rows_compact_kernel(float* __restrict__ grad, int rows, int cols, int cap,
     int n = 0;
     const bool vec = (cols % 4) == 0 && ((reinterpret_cast<uintptr_t>(g) & 15u) == 0);
     if (vec) {
-        for (int c0 = 0; c0 < cols; c0 += 128) {
-            const int c = c0 + 4 * lane;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (c < cols) v = *reinterpret_cast<const float4*>(g + c);
-            const float e[4] = {v.x, v.y, v.z, v.w};
-            const int mine = (e[0] != 0.f) + (e[1] != 0.f) + (e[2] != 0.f) + (e[3] != 0.f);
-            if (__any_sync(0xffffffffu, mine != 0)) {
-                // exclusive prefix of `mine` over the lanes: ascending column order
-                int incl = mine;
+        // four 512-byte pieces of the row in flight per warp before the first vote
+        for (int c00 = 0; c00 < cols; c00 += 512) {
+            float4 vs[4];
 #pragma unroll
-                for (int d = 1; d < 32; d <<= 1) {
-                    const int t = __shfl_up_sync(0xffffffffu, incl, d);
-                    if (lane >= d) incl += t;
-                }
-                int at = n + incl - mine;
+            for (int u = 0; u < 4; ++u) {
+                const int c = c00 + 128 * u + 4 * lane;
+                vs[u] = c < cols ? *reinterpret_cast<const float4*>(g + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    if (e[k] != 0.f) {
-                        if (at < cap) out[at] = Entry{c + k, e[k]};
-                        ++at;
+            for (int u = 0; u < 4; ++u) {
+                const int c = c00 + 128 * u + 4 * lane;
+                const float e[4] = {vs[u].x, vs[u].y, vs[u].z, vs[u].w};
+                const int mine = (e[0] != 0.f) + (e[1] != 0.f) + (e[2] != 0.f) + (e[3] != 0.f);
+                if (__any_sync(0xffffffffu, mine != 0)) {
+                    // exclusive prefix of `mine` over the lanes: ascending column order
+                    int incl = mine;
+#pragma unroll
+                    for (int d = 1; d < 32; d <<= 1) {
+                        const int t = __shfl_up_sync(0xffffffffu, incl, d);
+                        if (lane >= d) incl += t;
                     }
-                if (mine) *reinterpret_cast<float4*>(g + c) = make_float4(0.f, 0.f, 0.f, 0.f);
-                n += __shfl_sync(0xffffffffu, incl, 31);
+                    int at = n + incl - mine;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        if (e[k] != 0.f) {
+                            if (at < cap) out[at] = Entry{c + k, e[k]};
+                            ++at;
+                        }
+                    if (mine) *reinterpret_cast<float4*>(g + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+                    n += __shfl_sync(0xffffffffu, incl, 31);
+                }
             }
         }
     } else {
