@@ -116,30 +116,31 @@ inf_backward_weight_accum_kernel(const float* __restrict__ gout, const int* __re
     // staging area behind the rows: [rpc][SBP] pos words, [rpc][SBP] signed values
     int* spos = reinterpret_cast<int*>(smem_f + (size_t)rpc * row_words);
     float* sval = reinterpret_cast<float*>(spos + (size_t)rpc * SBP);
+    const int sj = threadIdx.x % rpc, se = threadIdx.x / rpc;          // staging: this thread's row and first source
+    const size_t srow = (size_t)min(row0 + sj, n_rows - 1);
     for (int s0 = 0; s0 < n_src; s0 += SB) {
         const int cnt = min(SB, n_src - s0);
-        const int total = cnt * rpc;
         constexpr int SU = 8;                             // loads in flight per thread
-        for (int q0 = threadIdx.x; q0 < total; q0 += SU * blockDim.x) {
+        // element q = e * rpc + j of the block (source e of row j) goes to thread q mod blockDim; blockDim is
+        // 32 * rpc, so a thread keeps its row j = sj and meets the sources se, se + 32, se + 64, ...
+        for (int eb = se; eb < cnt; eb += 32 * SU) {
             int pp[SU]; float pg[SU];
 #pragma unroll
             for (int u = 0; u < SU; ++u) {
-                const int q = q0 + u * blockDim.x;
+                const int e = eb + 32 * u;
                 pp[u] = -1; pg[u] = 0.f;
-                if (q < total) {
-                    const int j = q % rpc, e = q / rpc;
+                if (e < cnt) {
                     // source r of row (g, o): element (r * G + g) * COg + o = r * CO + row
-                    const size_t a = (size_t)(s0 + e) * d.CO + min(row0 + j, n_rows - 1);
+                    const size_t a = (size_t)(s0 + e) * d.CO + srow;
                     pp[u] = __ldg(pos + a); pg[u] = __ldg(gout + a);
                 }
             }
 #pragma unroll
             for (int u = 0; u < SU; ++u) {
-                const int q = q0 + u * blockDim.x;
-                if (q < total) {
-                    const int j = q % rpc, e = q / rpc;
-                    spos[j * SBP + e] = pp[u];
-                    sval[j * SBP + e] = (pp[u] >= 0) ? -pg[u] : pg[u];    // grad_weight takes -s * g
+                const int e = eb + 32 * u;
+                if (e < cnt) {
+                    spos[sj * SBP + e] = pp[u];
+                    sval[sj * SBP + e] = (pp[u] >= 0) ? -pg[u] : pg[u];    // grad_weight takes -s * g
                 }
             }
         }
