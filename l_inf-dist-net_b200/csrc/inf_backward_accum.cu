@@ -116,6 +116,7 @@ inf_backward_weight_accum_kernel(const float* __restrict__ gout, const int* __re
     // staging area behind the rows: [rpc][SBP] pos words, [rpc][SBP] signed values
     int* spos = reinterpret_cast<int*>(smem_f + (size_t)rpc * row_words);
     float* sval = reinterpret_cast<float*>(spos + (size_t)rpc * SBP);
+    int occupied = 0;                                                  // COMPACT: bins of this row that occur
     const int sj = threadIdx.x % rpc, se = threadIdx.x / rpc;          // staging: this thread's row and first source
     const size_t srow = (size_t)min(row0 + sj, n_rows - 1);
     for (int s0 = 0; s0 < n_src; s0 += SB) {
@@ -167,6 +168,7 @@ inf_backward_weight_accum_kernel(const float* __restrict__ gout, const int* __re
                     if (w0 + lane < nbw) before[w0 + lane] = run + incl - c;
                     run += __shfl_sync(FULL, incl, 31);
                 }
+                occupied = run;
                 __syncwarp();
             }
             // groups of 4 batches: the grouping of all four is issued before the first is added
@@ -193,6 +195,25 @@ inf_backward_weight_accum_kernel(const float* __restrict__ gout, const int* __re
     float* out = dst + (size_t)row * nb;
     if (COMPACT) {
         __syncwarp();
+        if (vec_out && occupied <= 64) {
+            // few bins occur (the usual case in training: the sources of a row agree on their arg-max position):
+            // four bins per lane and store, nearly all of them zero (53 against 57 us at B = 512, Din = Dout = 5120;
+            // with hundreds of occurring bins the word-by-word loop below is the faster one, 63 against 69 us)
+            for (int i = lane * 4; i < nb; i += 128) {
+                const unsigned word = bits[i >> 5];
+                const unsigned nib = (word >> (i & 31)) & 0xfu;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (nib) {
+                    int at = before[i >> 5] + __popc(word & ((1u << (i & 31)) - 1u));
+                    if (nib & 1u) v.x = acc[at++];
+                    if (nib & 2u) v.y = acc[at++];
+                    if (nib & 4u) v.z = acc[at++];
+                    if (nib & 8u) v.w = acc[at];
+                }
+                *reinterpret_cast<float4*>(out + i) = v;
+            }
+            return;
+        }
         for (int i0 = 0; i0 < nb; i0 += 32) {
             const unsigned word = bits[i0 >> 5];
             const int i = i0 + lane;
