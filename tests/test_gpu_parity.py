@@ -865,3 +865,17 @@ def test_training_step_with_and_without_fused_mean_shift(cuda, lib):
         L.set_fused_epilogue(True)
     for qa, qb in zip(a, b):
         torch.testing.assert_close(qa, qb, rtol=1e-4, atol=1e-5)
+
+
+def test_launch_count_counts_the_library_kernels(cuda, lib):
+    """linf_launch_count: what bench.py reports as gpu_launches.  A forward and the two backward kernels of the
+    headline layer are three launches; a call that is refused launches nothing."""
+    x, w, g = make_inputs(64, 784, 256, 1, 1, seed=5)
+    n0 = lib.linf_launch_count()
+    y, pos = c_inf_forward(dev(x), dev(w), 1, use_ws=False)
+    n1 = lib.linf_launch_count()
+    c_inf_backward(dev(g), pos, 784, 1, "both")
+    n2 = lib.linf_launch_count()
+    assert 1 <= n1 - n0 <= 2 and n2 - n1 == 2, (n0, n1, n2)
+    assert lib.linf_inf_dist_forward(None, None, 1, 1, 1, 1, 1, None, None, None) != 0
+    assert lib.linf_launch_count() == n2
