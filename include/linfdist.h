@@ -310,6 +310,8 @@ int linf_grad_rows_merge(float* grad, int rows, int cols, int cap, const int* co
  *   key 5  width of the forward's output tiles: 0 = by shape (default), 1 = 64 columns, 2 = 48 columns wherever
  *          that kernel applies
  *   key 6  the same for the finite-p forward
+ *   key 7  arg-max tracking windows of the forward: 0 = 16 terms for rows of 2048 terms and more, else 8 (default),
+ *          1 = 8 terms always
  * Returns LINF_OK, the answer of key 2, or LINF_ERR_DIMS for an unknown key / value.
  */
 int linf_tune_set(int key, int value);

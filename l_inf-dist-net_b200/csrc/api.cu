@@ -86,6 +86,7 @@ extern int inf_forward_variant;
 extern int inf_forward_tail;
 extern int inf_forward_split;
 extern int inf_forward_width;
+extern int inf_forward_windows;
 extern int lp_forward_width;
 int inf_forward_tma_gave_up();
 
@@ -128,6 +129,7 @@ int linf_tune_set(int key, int value) {
     if (key == 4 && value >= 0 && value <= 2) { inf_forward_split = value; return LINF_OK; }
     if (key == 5 && value >= 0 && value <= 2) { inf_forward_width = value; return LINF_OK; }
     if (key == 6 && value >= 0 && value <= 2) { lp_forward_width = value; return LINF_OK; }
+    if (key == 7 && value >= 0 && value <= 1) { inf_forward_windows = value; return LINF_OK; }
     if (key == 2) return inf_forward_tma_gave_up();   // 1 = a bounded wait of the TMA loader ran out since the library was loaded
     return LINF_ERR_DIMS;
 }

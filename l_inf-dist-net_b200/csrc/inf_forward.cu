@@ -614,6 +614,7 @@ struct Variant {
     Kernels tail;      // 64 x 32 output tiles (8 x 2 outputs per thread) for a partial last wave
     int tma;           // 0: cp.async loader; 1: TMA, padded boxes; 2: TMA, 128-byte swizzle
     Kernels narrow;    // 64 x 48 output tiles (8 x 3 outputs per thread), 3 CTAs per SM, loader of `main`; nt == 0: none
+    Kernels main_long, narrow_long;   // the same two with 16-term tracking windows, for long rows; nt == 0: none
 };
 constexpr Kernels kNoKernels{0, 0, 0, 0, 0, 0, nullptr, nullptr};
 
@@ -633,18 +634,24 @@ constexpr Kernels make_kernels() {
 // with the register budget of 4 CTAs per SM (spills 108 bytes): 189 / 232 / 617 / 1004.
 const Variant kVariants[] = {
     // 0: 32-term k-tiles fetched by TMA with the 128-byte swizzle (unpadded rows, 3 stages), 8-term windows (default)
+    //    Rows of 2048 terms and more: 16-term windows (half the tracking instructions, a rescan of 128 instead of
+    //    64 bytes per output): 565 / 907 us at Din = 3072 / 5120 against 586 / 952 us, 1081 against 1153 us at
+    //    B = 256, Din = 12288; equal at Din = 1536, 8 % slower at Din = 784.  32-term windows lose everywhere
+    //    (625 / 947 us; 257 us at Din = 784).
     {make_kernels<Geo<128, 4, 32, 3, 8, 0>, 2>(), make_kernels<Geo<128, 2, 32, 4, 8>>(), 2,
-     make_kernels<Geo<128, 3, 32, 3, 8, 0>, 2>()},
+     make_kernels<Geo<128, 3, 32, 3, 8, 0>, 2>(),
+     make_kernels<Geo<128, 4, 32, 3, 16, 0>, 2>(), make_kernels<Geo<128, 3, 32, 3, 16, 0>, 2>()},
     // 1: 32-term k-tiles (cp.async, 3 stages), 8-term tracking windows
-    {make_kernels<Geo<128, 4, 32, 3, 8>>(), make_kernels<Geo<128, 2, 32, 4, 8>>(), 0, kNoKernels},
+    {make_kernels<Geo<128, 4, 32, 3, 8>>(), make_kernels<Geo<128, 2, 32, 4, 8>>(), 0, kNoKernels, kNoKernels, kNoKernels},
     // 2: 16-term k-tiles (cp.async, 4 stages), 8-term tracking windows
-    {make_kernels<Geo<128, 4, 16, 3, 8>>(), make_kernels<Geo<128, 2, 16, 4, 8>>(), 0, kNoKernels},
+    {make_kernels<Geo<128, 4, 16, 3, 8>>(), make_kernels<Geo<128, 2, 16, 4, 8>>(), 0, kNoKernels, kNoKernels, kNoKernels},
     // 3: 16-term k-tiles, one tracking window per k-tile
-    {make_kernels<Geo<128, 4, 16, 3, 16>>(), make_kernels<Geo<128, 2, 16, 4, 16>>(), 0, kNoKernels},
+    {make_kernels<Geo<128, 4, 16, 3, 16>>(), make_kernels<Geo<128, 2, 16, 4, 16>>(), 0, kNoKernels, kNoKernels, kNoKernels},
     // 4: as 3 with TMA and padded boxes (measured 7-14 % slower than 3: the extra four columns per row cost L2
     //    traffic)
-    {make_kernels<Geo<128, 4, 16, 3, 16>, 1>(), make_kernels<Geo<128, 2, 16, 4, 16>>(), 1, kNoKernels},
+    {make_kernels<Geo<128, 4, 16, 3, 16>, 1>(), make_kernels<Geo<128, 2, 16, 4, 16>>(), 1, kNoKernels, kNoKernels, kNoKernels},
 };
+constexpr int kLongRow = 2048;      // rows from this length on take the kernels with 16-term tracking windows
 constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
 
 }  // namespace
@@ -660,6 +667,7 @@ int inf_forward_tma_gave_up() {
 int inf_forward_variant = 0;   // index into kVariants (benchmarking knob)
 int inf_forward_tail = 1;      // 1: a partial last wave runs as half-width tiles; 0: never
 int inf_forward_split = 0;     // 0: k-splitting by the rule of make_plan; 1: whenever scratch is given; 2: never
+int inf_forward_windows = 0;   // 0: 16-term tracking windows for long rows; 1: 8-term windows always (benchmarking knob)
 int inf_forward_width = 0;     // 0: tile width by the rule of make_plan; 1: 64 columns always; 2: 48 wherever they exist
 
 // Shapes the tiled path accepts (window numbers travel as 16 bits: at most 65535 windows per row).
@@ -814,7 +822,9 @@ int inf_forward(const float* x, const float* w, const Dims& d, float* y, int* po
     p.x = x; p.w = w; p.y = y; p.pos = pos;
     p.M = d.R; p.N = d.COg; p.K = d.CIg; p.G = d.G;
     p.lda = d.CI; p.ldo = d.CO;
-    const Kernels* use = plan.narrow ? &v.narrow : &v.main;
+    // (not with the k-split: 430 against 416 us at B = 512, Din = 5120, Dout = 2048, 311 against 291 us at B = 128)
+    const bool long_rows = d.CIg >= kLongRow && v.main_long.nt != 0 && inf_forward_windows != 1 && !plan.split;
+    const Kernels* use = plan.narrow ? (long_rows ? &v.narrow_long : &v.narrow) : (long_rows ? &v.main_long : &v.main);
     if (v.tma) {
         const int pad = v.tma == 1 ? 4 : 0;
         const bool ok = tma_shape_ok(d, use->bk) &&

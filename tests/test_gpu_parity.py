@@ -643,7 +643,9 @@ def test_inf_forward_other_loader_variants(cuda, lib, shape, variant):
 
 @pytest.mark.parametrize("shape", [(64, 64, 64, 1, 1), (33, 100, 65, 1, 1), (130, 784, 200, 1, 1), (16, 64, 256, 1, 4),
                                    (70, 1000, 96, 1, 1), (512, 784, 640, 1, 1), (64, 3072, 512, 1, 4), (9, 36, 40, 1, 1),
-                                   (200, 256, 48, 1, 1), (65, 160, 49, 1, 1), (300, 1024, 1100, 1, 1)], ids=_ids)
+                                   (200, 256, 48, 1, 1), (65, 160, 49, 1, 1), (300, 1024, 1100, 1, 1),
+                                   # rows of 2048 terms and more: 16-term tracking windows
+                                   (70, 2304, 130, 1, 1), (33, 4100, 96, 1, 1), (40, 4096, 128, 1, 2)], ids=_ids)
 @pytest.mark.parametrize("width", [1, 2], ids=["tiles_64", "tiles_48"])
 def test_inf_forward_tile_widths(cuda, lib, shape, width):
     """The library picks between output tiles of 64 x 64 and 64 x 48 (and k-splitting) by the shape; forced either
@@ -654,14 +656,16 @@ def test_inf_forward_tile_widths(cuda, lib, shape, width):
     y_ref, pos_ref = oracle.inf_dist_forward(x, w, G)
     assert lib.linf_tune_set(5, width) == 0
     try:
-        for split in (2, 0, 1):
-            assert lib.linf_tune_set(4, split) == 0
-            for use_ws in (False, True):
-                y, pos = c_inf_forward(dev(x), dev(w), G, use_ws=use_ws)
-                assert_bits_equal(y, y_ref, "values"); assert_bits_equal(pos, pos_ref, "arg-max")
+        for windows in ((0, 1) if CI // G >= 2048 else (0,)):
+            assert lib.linf_tune_set(7, windows) == 0
+            for split in (2, 0, 1):
+                assert lib.linf_tune_set(4, split) == 0
+                for use_ws in (False, True):
+                    y, pos = c_inf_forward(dev(x), dev(w), G, use_ws=use_ws)
+                    assert_bits_equal(y, y_ref, "values"); assert_bits_equal(pos, pos_ref, "arg-max")
         assert lib.linf_tune_set(2, 0) == 0
     finally:
-        lib.linf_tune_set(5, 0); lib.linf_tune_set(4, 0)
+        lib.linf_tune_set(5, 0); lib.linf_tune_set(4, 0); lib.linf_tune_set(7, 0)
 
 
 def test_adamw_step_rows_equals_whole_tensor_step(cuda, lib):
