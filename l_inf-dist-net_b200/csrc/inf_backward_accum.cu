@@ -153,7 +153,7 @@ inf_backward_weight_accum_kernel(const float* __restrict__ gout, const int* __re
                 // which bins occur, and how many occurring bins lie before each 32-bin word
                 for (int e = lane; e < cnt; e += 32) {
                     const int idx = mp[e] & 0x7fffffff;
-                    if (idx < nb) atomicOr(&bits[idx >> 5], 1u << (idx & 31));
+                    if (idx < nb && mv[e] != 0.f) atomicOr(&bits[idx >> 5], 1u << (idx & 31));
                 }
                 __syncwarp();
                 int run = 0;
@@ -177,12 +177,15 @@ inf_backward_weight_accum_kernel(const float* __restrict__ gout, const int* __re
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     const int e = (b0 + u) * 32 + lane;
-                    int idx = e < cnt ? (mp[e] & 0x7fffffff) : 0x7fffffff;
+                    const float val = e < cnt ? mv[e] : 0.f;
+                    // a source whose value is +-0 changes no sum (the accumulators start at +0 and can never become -0):
+                    // it is dropped, which is most sources of most rows in a training step
+                    int idx = (e < cnt && val != 0.f) ? (mp[e] & 0x7fffffff) : 0x7fffffff;
                     if (COMPACT) {
                         // dense number of the bin among the occurring ones (equal bins, equal numbers)
                         idx = idx < nb ? before[idx >> 5] + __popc(bits[idx >> 5] & ((1u << (idx & 31)) - 1u)) : 0x7fffffff;
                     }
-                    bt[u] = classify(idx, e < cnt ? mv[e] : 0.f, COMPACT ? SB : nb, lane);
+                    bt[u] = classify(idx, val, COMPACT ? SB : nb, lane);
                 }
 #pragma unroll
                 for (int u = 0; u < 4; ++u)

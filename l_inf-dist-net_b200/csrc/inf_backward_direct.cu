@@ -50,7 +50,7 @@ inf_backward_input_direct_kernel(const float* __restrict__ gout, const int* __re
         if (s0 + S + tid < n_src) { p_next = __ldg(p_row + s0 + S + tid); g_next = __ldg(g_row + s0 + S + tid); }
         const int idx = p & 0x7fffffff;
         const float v = (p >= 0) ? gv : -gv;                    // grad_input takes +s * g
-        bool pending = have && idx < nb;
+        bool pending = have && idx < nb && v != 0.f;           // +-0 changes no sum (accumulators start at +0, never become -0)
         int more = 1;
 #pragma unroll 1
         for (int round = 0; round < MAX_ROUNDS && more; ++round) {

@@ -590,6 +590,24 @@ def test_inf_backward_synthetic_positions(cuda, lib, pattern, shape):
         assert_bits_equal(gx, gx_ref, f"{mode} grad_input"); assert_bits_equal(gw, gw_ref, f"{mode} grad_weight")
 
 
+@pytest.mark.parametrize("shape", [(512, 784, 5120), (96, 3072, 1024), (64, 5120, 1024), (40, 2048, 1536), (300, 100, 65)],
+                         ids=lambda s: "B{}_CI{}_CO{}".format(*s))
+def test_inf_backward_with_mostly_zero_grad_output(cuda, lib, shape):
+    """In a training step most of grad_output is exactly zero (whole columns of it).  The kernels drop such sources
+    instead of adding +-0; the sums must still be the checker's bits, signed zeros included."""
+    B, CI, CO = shape
+    x, w, _ = make_inputs(B, CI, CO, 1, 1, seed=4000 + CO)
+    _, pos = oracle.inf_dist_forward(x, w, 1)
+    rng = np.random.default_rng(B + CO)
+    g = rng.standard_normal((B, CO, 1)).astype(np.float32)
+    g[:, rng.random(CO) < 0.9, :] = 0.0                      # nine columns in ten are zero
+    g[rng.random((B, CO, 1)) < 0.3] *= 0.0                   # and a third of the rest, as +0 or -0
+    gx_ref, gw_ref = oracle.inf_dist_backward(g, pos, CI, 1)
+    for mode in ("ordered", "both"):
+        gx, gw = c_inf_backward(dev(g), dev(pos), CI, 1, mode)
+        assert_bits_equal(gx, gx_ref, f"{mode} grad_input"); assert_bits_equal(gw, gw_ref, f"{mode} grad_weight")
+
+
 @pytest.mark.parametrize("pattern", ["hot", "spread", "mixed"])
 def test_inf_backward_input_kernel_choice(cuda, lib, pattern):
     """grad_input of a wide dense layer runs on the direct-accumulation kernel or on the sort kernel, as a probe of
