@@ -22,9 +22,12 @@
  *     ever traps or asserts on the device;
  *   - besides cached per-device attributes the library keeps one helper stream per device
  *     (linf_inf_dist_backward runs its second kernel there); its fork / join events are queued
- *     under a per-device lock, so calls from several host threads are safe.  The tuning hook
- *     linf_tune_set at the end of this header is the exception: it is process-wide and not
- *     thread safe.
+ *     under a per-device lock, so calls from several host threads are safe.  The grad_input
+ *     kernels of wide dense layers pick their algorithm from a probe of the data; the probe's
+ *     verdict travels in a slot of a small array inside the library, one slot per call, reused
+ *     after 256 calls (so at most 256 such calls may be in flight on a device at once).  The
+ *     tuning hook linf_tune_set at the end of this header is the exception: it is process-wide
+ *     and not thread safe.
  */
 #ifndef LINFDIST_H_
 #define LINFDIST_H_
