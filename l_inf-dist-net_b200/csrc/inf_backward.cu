@@ -359,8 +359,11 @@ inf_backward_rows_kernel(const float* __restrict__ gout, const int* __restrict__
     __syncthreads();
 #pragma unroll
     for (int j = 0; j < EPT; ++j) {
+        // a source that adds +-0 changes no sum (every bin starts at +0 and can never become -0): it is dropped
+        // here and at the placement, like an index outside the group
+        if (gv[j] == 0.f) pv[j] = 0x7fffffff;
         const int idx = pv[j] & 0x7fffffff;
-        if (idx < nb) atomicAdd(&myhist[idx], 1);        // an index outside the group is dropped
+        if (idx < nb) atomicAdd(&myhist[idx], 1);
     }
     __syncthreads();
     // ---- 2. first slot of every bin (and of every copy's share of the bin) ----
